@@ -41,6 +41,9 @@ class PagedKVNeed:
   stride: int = 1
   # Storage type where it is not the activations' ("float32").
   dtype: str | None = None
+  # True: an entry has one row of head_dim numbers, whose first value_dim are its value as well
+  # (a cache of latents that are key and value at once); a page then holds key rows only.
+  values_in_keys: bool = False
 
   @property
   def v_dim(self) -> int:
@@ -53,6 +56,8 @@ class PagedKVNeed:
     """Per page all key rows `[num_kv_heads, entries, head_dim]`, then all value rows
     `[num_kv_heads, entries, v_dim]`; with equal sizes that is `[2, heads, entries, head_dim]`."""
     entries = self.entries_per_page(page_size)
+    if self.values_in_keys:
+      return (num_pages, self.num_kv_heads * entries * self.head_dim)
     if self.v_dim == self.head_dim:
       return (num_pages, 2, self.num_kv_heads, entries, self.head_dim)
     return (num_pages, self.num_kv_heads * entries * (self.head_dim + self.v_dim))

@@ -10,6 +10,7 @@ from simply_b200.config.engine_config import EngineConfig
 from simply_b200.config.gemma2 import ConfigError, Gemma2Config
 from simply_b200.config.generax import GeneraxConfig
 from simply_b200.config.sapivik import SapivikConfig
+from simply_b200.config.zesapel import ZesapelConfig
 from simply_b200.config.model_spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 from simply_b200.registry import ARCHITECTURES
 
@@ -61,6 +62,6 @@ def preset(name: str):
 
 __all__ = [
     "ConfigError", "EngineConfig", "Gemma2Config", "GeneraxConfig", "LayerCall", "LayerSpec", "ModelSpec",
-    "PartSpec", "SapivikConfig", "config_from_dict", "load_config", "preset", "preset_dict", "preset_names",
+    "PartSpec", "SapivikConfig", "ZesapelConfig", "config_from_dict", "load_config", "preset", "preset_dict", "preset_names",
     "read_config_json",
 ]

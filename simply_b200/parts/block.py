@@ -40,6 +40,43 @@ class ResidualStream:
     self._branch: torch.Tensor | None = None
     self._post: Norm | None = None
     self._second: torch.Tensor | None = None
+    # A stream that is kept several times (`hyper_connection` blocks): float32 [T, copies, width]
+    # in place of `h`, and the write that is still to be done (branch, mix [from, to], out [to]).
+    self.lanes: torch.Tensor | None = None
+    self._lane_write: tuple | None = None
+
+  # ---- a stream kept several times ------------------------------------------------------------
+  def spread(self, copies: int, ctx: Any) -> None:
+    """From here on the stream is `copies` equal copies of what it holds now."""
+    if self.lanes is None:
+      self.flush(ctx)
+      self.lanes = ctx.ops.spread_streams(self.h, copies)
+      self.h = None
+    elif self.lanes.shape[1] != copies:
+      raise ValueError(f"the stream is kept {self.lanes.shape[1]} times, a block wants {copies}")
+
+  def write_lanes(self, branch: torch.Tensor, mix: torch.Tensor, out: torch.Tensor, ctx: Any) -> None:
+    """copy_t <- sum_s mix[s, t] copy_s + out[t] * branch, done when the stream is next read."""
+    self.flush(ctx)
+    self._lane_write = (branch, mix, out)
+
+  def read_lanes(self, weights: torch.Tensor | None, norm: Norm | None, ctx: Any,
+                 rows: torch.Tensor | None = None) -> torch.Tensor | None:
+    """norm(sum_s weights[s] copy_s) in the activation dtype after the pending write, in one kernel."""
+    branch, mix, out = self._lane_write or (None, None, None)
+    if norm is not None and not isinstance(norm, RMSNorm):
+      raise TypeError("a stream kept several times is read through an RMS norm")
+    y = ctx.ops.streams_step(self.lanes, branch, mix, out, weights, norm.weight if norm is not None else None,
+                             norm.eps if norm is not None else 0.0, bool(norm.plus_one) if norm is not None else False,
+                             rows)
+    if rows is None:
+      self._lane_write = None
+    return y
+
+  def total(self, ctx: Any) -> torch.Tensor:
+    """The stream as one float32 [T, width] (the sum of its copies); a new tensor."""
+    self.flush(ctx)
+    return self.h.clone() if self.lanes is None else self.lanes.sum(dim=1)
 
   def add(self, branch: torch.Tensor, post_norm: Norm | None, ctx: Any) -> None:
     if self._branch is not None and self._second is None and post_norm is None:
@@ -58,13 +95,23 @@ class ResidualStream:
       self.add(x, None, ctx)
 
   def flush(self, ctx: Any) -> None:
+    if self._lane_write is not None:
+      self.read_lanes(None, None, ctx)
     if self._branch is not None:
       self._combine(None, ctx, None)
 
   def normed(self, norm: Norm, ctx: Any, rows: torch.Tensor | None = None) -> torch.Tensor:
     """norm(h + pending) in the activation dtype.  With `rows`, only those rows are
     computed and returned (the stream is then left as it is: use this last)."""
+    if self.lanes is not None:
+      return self.read_lanes(self._ones(ctx), norm, ctx, rows)
     return self._combine(norm, ctx, rows)
+
+  def _ones(self, ctx: Any) -> torch.Tensor:
+    key = ("stream_ones", self.lanes.shape[1])
+    if key not in ctx.memo:
+      ctx.memo[key] = torch.ones(self.lanes.shape[1], dtype=torch.float32, device=self.lanes.device)
+    return ctx.memo[key]
 
   def _combine(self, pre: Norm | None, ctx: Any, rows: torch.Tensor | None):
     ops = ctx.ops

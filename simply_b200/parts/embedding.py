@@ -23,25 +23,44 @@ class TokenEmbedding(Embedding):
 
   graph_safe = True
 
-  def __init__(self, prefix: str, vocab_size: int, width: int, scale: float = 1.0, name: str | None = None):
+  def __init__(self, prefix: str, vocab_size: int, width: int, scale: float = 1.0, name: str | None = None,
+               position_table: str | None = None, max_positions: int = 0, round_scale: bool = True):
+    """`position_table`: name of a learned table [max_positions, width] whose row `position` is added
+    (unscaled) to every token's row.  `round_scale`: the factor is rounded to the table's dtype first
+    (the reference's way); False multiplies by the float32 factor."""
     self.name = name or f"{prefix}.weight"
     self.vocab_size = vocab_size
     self.width = width
     self.scale = float(scale)
+    self.round_scale = bool(round_scale)
+    self.position_name, self.max_positions = position_table, int(max_positions)
+    if position_table is not None and self.max_positions <= 0:
+      raise ValueError(f"{prefix}: a position table needs max_positions")
     self.table: torch.Tensor | None = None
+    self.positions: torch.Tensor | None = None
 
   def tensor_specs(self) -> list[TensorSpec]:
-    return [TensorSpec(self.name, (self.vocab_size, self.width), "matrix")]
+    specs = [TensorSpec(self.name, (self.vocab_size, self.width), "matrix")]
+    if self.position_name is not None:
+      specs.append(TensorSpec(self.position_name, (self.max_positions, self.width), "matrix"))
+    return specs
 
   def bind(self, tensors, ops) -> None:
     self.table = tensors[self.name]
+    if self.position_name is not None:
+      self.positions = tensors[self.position_name]
 
   def forward(self, ctx: Any) -> torch.Tensor:
     """float32 [T, width]: the start of the residual stream."""
-    return ctx.ops.embed(self.table, ctx.token_ids, self.scale)
+    if self.positions is None and self.round_scale:
+      return ctx.ops.embed(self.table, ctx.token_ids, self.scale)
+    return ctx.ops.embed(self.table, ctx.token_ids, self.scale, positions=ctx.positions,
+                         position_table=self.positions, round_scale=self.round_scale)
 
   def rides_exactly(self, dtype: torch.dtype) -> bool:
     """True if `forward`'s float32 rows are exact in `dtype` (rows of the table as they are)."""
+    if self.positions is not None and dtype != torch.float32:
+      return False
     return dtype == torch.float32 or (self.scale == 1.0 and self.table is not None and self.table.dtype == dtype)
 
 

@@ -107,3 +107,42 @@ class RoutedExperts(FeedForward):
       shared = self.shared[2](ops.gated_linear(x, self.shared_gate_up, self.activation), ctx)
     return ops.mix_experts(x, chosen, weight, self.gate_up, self.down, self.num_experts, self.activation,
                            shared, gate)
+
+
+@FEED_FORWARDS.register("table_experts")
+class TableExperts(FeedForward):
+  """Experts without a router: a table `table` [vocab, top] of integers gives each token id its
+  `top` experts (the entries of a row differ), each with weight 1 / top.  An expert is
+  W_down act(W_up y), without biases and without a gate; `activation` "gelu_erf" is the exact gelu."""
+
+  graph_safe = True  # the table is read on the device
+
+  def __init__(self, prefix: str, width: int, hidden: int, num_experts: int, top: int, vocab_size: int,
+               activation: str = "gelu_erf", names: dict[str, str] | None = None):
+    if not 1 <= top <= num_experts:
+      raise ValueError(f"{prefix}: each token uses {top} of {num_experts} experts")
+    self.prefix, self.width, self.hidden = prefix, width, hidden
+    self.num_experts, self.top, self.vocab_size = num_experts, top, vocab_size
+    self.activation = ACTIVATIONS.get(activation)
+    if self.activation == 3:
+      raise ValueError(f"{prefix}: the clamped activation acts on a gate and an up half; these experts have no gate")
+    n = self.names = {"up": "up", "down": "down", "expert": "e", "table": "table", **(names or {})}
+    self.experts = [(Linear(f"{prefix}.{n['expert']}{e}.{n['up']}", hidden, width),
+                     Linear(f"{prefix}.{n['expert']}{e}.{n['down']}", width, hidden)) for e in range(num_experts)]
+    self.table_name = f"{prefix}.{n['table']}"
+    self.up = self.down = self.table = None
+
+  def tensor_specs(self) -> list[TensorSpec]:
+    specs = [p.spec() for pair in self.experts for p in pair]
+    return specs + [TensorSpec(self.table_name, (self.vocab_size, self.top), "table", choices=self.num_experts)]
+
+  def bind(self, tensors, ops) -> None:
+    self.up = torch.stack([tensors[u.name] for u, _ in self.experts]).contiguous()
+    self.down = torch.stack([tensors[d.name] for _, d in self.experts]).contiguous()
+    self.table = tensors[self.table_name].to(torch.int32).contiguous()
+
+  def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
+    ops = ctx.ops
+    chosen, weight = ops.route_by_table(ctx.token_ids, self.table, self.num_experts)
+    return ops.mix_experts(x, chosen, weight, self.up, self.down, self.num_experts, self.activation, None, None,
+                           gated=False)

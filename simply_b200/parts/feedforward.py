@@ -23,6 +23,7 @@ ACTIVATIONS.register("gelu_tanh", 0)
 ACTIVATIONS.register("silu", 1)
 ACTIVATIONS.register("relu", 2)
 ACTIVATIONS.register("clamped_swish", 3)
+ACTIVATIONS.register("gelu_erf", 4)  # the exact gelu; experts without a gate only
 
 
 @FEED_FORWARDS.register("gated")
@@ -36,6 +37,8 @@ class GatedFeedForward(FeedForward):
     self.width = width
     self.hidden = hidden
     self.activation = ACTIVATIONS.get(activation)
+    if self.activation > 3:
+      raise ValueError(f"{prefix}: the gated products take gelu_tanh, silu, relu and clamped_swish")
     self.limit = float(limit)
     if activation == "clamped_swish" and not self.limit > 0:
       raise ValueError(f"{prefix}: the clamped activation needs a positive limit")

@@ -26,6 +26,10 @@ from simply_b200.parts import delta_rule as _delta_rule  # noqa: F401
 from simply_b200.parts import experts as _experts  # noqa: F401
 from simply_b200.parts import forget_gate as _forget_gate  # noqa: F401
 from simply_b200.parts import head_norm_attention as _head_norm_attention  # noqa: F401
+from simply_b200.parts import hyper_connection as _hyper_connection  # noqa: F401
+from simply_b200.parts import general_delta as _general_delta  # noqa: F401
+from simply_b200.parts import latent_attention as _latent_attention  # noqa: F401
+from simply_b200.parts import state_space as _state_space  # noqa: F401
 from simply_b200.parts import normed_attention as _normed_attention  # noqa: F401
 from simply_b200.parts import embedding as _embedding  # noqa: F401
 from simply_b200.parts import feedforward as _feedforward  # noqa: F401
@@ -117,8 +121,7 @@ class DecoderModel:
         stream.add_input(again, ctx)
       self.blocks[call.layer].forward(stream, ctx, caches.get(cache), call.writes_cache)
       if layer_outputs is not None:
-        stream.flush(ctx)
-        layer_outputs.append(stream.h.clone())
+        layer_outputs.append(stream.total(ctx))
     if ctx.logit_rows.numel() == 0:
       return None
     x = stream.normed(self.final_norm, ctx, rows=ctx.logit_rows)

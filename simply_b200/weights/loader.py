@@ -42,6 +42,8 @@ class TensorSpec:
     1) or "table" (integers).  The kind decides how random-weights mode fills it; the
     loader only uses it for integer tables.
   optional: may be absent from the files (e.g. a duplicate of a tied table).
+  choices: for an integer table, the number of values an entry may take (0 .. choices - 1) where
+    the entries of a row must differ; random-weights mode then draws every row without repetition.
   precision: "activation" (narrowed to the activation dtype on load), "stored" (a tensor stored
     in 32 bits stays in 32 bits) or None: "stored" for scales, "activation" otherwise.
   """
@@ -51,6 +53,7 @@ class TensorSpec:
   kind: str = "matrix"
   optional: bool = False
   precision: str | None = None
+  choices: int = 0
 
   def keeps_stored_precision(self) -> bool:
     if self.precision is None:

@@ -40,7 +40,11 @@ def random_tensors(
     gen = torch.Generator(device=device)
     gen.manual_seed((int(seed) << 20) + i)
     if s.kind == "table":
-      out[s.name] = torch.zeros(s.shape, dtype=torch.int32, device=device)
+      if s.choices > 0:  # every row: the first entries of a random order of the choices
+        order = torch.rand((s.shape[0], s.choices), generator=gen, device=device).argsort(dim=1)
+        out[s.name] = order[:, :s.shape[1]].to(torch.int32).contiguous()
+      else:
+        out[s.name] = torch.zeros(s.shape, dtype=torch.int32, device=device)
       continue
     if any(n < 0 for n in s.shape):
       raise ValueError(f"{s.name}: a size that only a file gives cannot be drawn at random; the configuration must name it")

@@ -43,11 +43,14 @@ class ReferenceOps:
   def check_errors(self):
     pass
 
-  def embed(self, table, ids, scale):
+  def embed(self, table, ids, scale, positions=None, position_table=None, round_scale=True):
     s = torch.tensor(scale, dtype=torch.float32)
-    if table.dtype == torch.bfloat16:
+    if table.dtype == torch.bfloat16 and round_scale:
       s = s.to(torch.bfloat16).float()
-    return table[ids.long()].float() * s
+    out = table[ids.long()].float() * s
+    if position_table is not None:
+      out = out + position_table[positions.long()].float()
+    return out
 
   def lm_head(self, x, table, cap):
     logits = x.float() @ table.float().t()
@@ -141,11 +144,11 @@ class ReferenceOps:
 
   # ---- attention ------------------------------------------------------------
   def paged_attention(self, q, storage, block_table, ctx, *, num_heads, num_kv_heads, head_dim,
-                      logit_softcap, window, value_dim=None, pooled=None):
-    if pooled is not None or (value_dim is not None and value_dim != head_dim):
+                      logit_softcap, window, value_dim=None, pooled=None, values_in_keys=False, sink=None):
+    if pooled is not None or (value_dim is not None and value_dim != head_dim) or values_in_keys or sink is not None:
       assert not logit_softcap
       return self._general_attention(q, storage, block_table, ctx, num_heads, num_kv_heads, head_dim,
-                                     value_dim or head_dim, window, pooled)
+                                     value_dim or head_dim, window, pooled, values_in_keys, sink)
     t = q.shape[0]
     out = torch.zeros(t, num_heads, head_dim, dtype=torch.float32, device=q.device)
     group = num_heads // num_kv_heads
@@ -244,10 +247,14 @@ class ReferenceOps:
     return y.reshape(t, num_heads * dim).to(self.dtype)
 
   def _general_attention(self, q, storage, block_table, ctx, num_heads, num_kv_heads, head_dim, value_dim,
-                         window, pooled):
+                         window, pooled, values_in_keys=False, sink=None):
     t = q.shape[0]
     ps = ctx.page_size
-    keys, values = self._kv_views(storage, num_kv_heads, ps, head_dim, value_dim)
+    if values_in_keys:  # one row per entry: the key, whose first value_dim numbers are the value
+      keys = storage.view(storage.shape[0], num_kv_heads, ps, head_dim)
+      values = keys[..., :value_dim]
+    else:
+      keys, values = self._kv_views(storage, num_kv_heads, ps, head_dim, value_dim)
     group = num_heads // num_kv_heads
     out = torch.zeros(t, num_heads, value_dim, dtype=torch.float32, device=q.device)
     q = q.reshape(t, num_heads, head_dim)
@@ -275,7 +282,11 @@ class ReferenceOps:
             v = torch.cat([pv[pg, :, e, :].float(), v], dim=0)
         for n in range(num_heads):
           m = n // group
-          p = torch.softmax(k[:, m] @ q[r, n].float(), dim=0)
+          scores = k[:, m] @ q[r, n].float()
+          if sink is None:
+            p = torch.softmax(scores, dim=0)
+          else:  # the denominator also holds exp(sink[n]), which has no value
+            p = torch.softmax(torch.cat([scores, sink[n].float().reshape(1)]), dim=0)[:-1]
           out[r, n] = p @ v[:, m]
     return out.reshape(t, num_heads * value_dim).to(self.dtype)
 
@@ -313,8 +324,9 @@ class ReferenceOps:
       storage[page, 1, :, pos % ps, :] = v.to(storage.dtype)
     return (prepare(q) * q_scale).to(self.dtype)
 
-  def sigmoid_gate(self, x, proj, offset):
-    return (x.float() * torch.sigmoid(proj[:, offset:offset + x.shape[1]].float())).to(self.dtype)
+  def sigmoid_gate(self, x, proj, offset, per=1):
+    gate = torch.sigmoid(proj[:, offset:offset + x.shape[1] // per].float())
+    return (x.float() * gate.repeat_interleave(per, dim=1)).to(self.dtype)
 
   # ---- forget-gate recurrence -----------------------------------------------------
   def forget_gate_scan(self, pre, bias, lower, state, ctx, *, num_heads, head_dim, value_dim):
@@ -346,13 +358,28 @@ class ReferenceOps:
     gate = torch.sigmoid(x.float() @ shared_gate_w.float()) if shared_gate_w is not None else None
     return chosen.to(torch.int32), weight, gate
 
-  def mix_experts(self, x, chosen, weight, gate_up, down, num_experts, activation, shared, shared_gate):
+  @staticmethod
+  def _activation(g, activation):
+    if activation == 4:
+      return 0.5 * g * (1.0 + torch.erf(g / math.sqrt(2.0)))
+    if activation == 0:
+      return 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))
+    return g * torch.sigmoid(g) if activation == 1 else torch.relu(g)
+
+  def route_by_table(self, token_ids, table, num_experts):
+    chosen = table[token_ids.long()].to(torch.int32)
+    return chosen, torch.full(chosen.shape, 1.0 / chosen.shape[1], dtype=torch.float32, device=chosen.device)
+
+  def mix_experts(self, x, chosen, weight, gate_up, down, num_experts, activation, shared, shared_gate, gated=True):
     xf = x.float()
     out = torch.zeros_like(xf)
     for t in range(x.shape[0]):
       for j in range(chosen.shape[1]):
         e = int(chosen[t, j])
-        if e < num_experts:
+        if e < num_experts and not gated:
+          h = self._activation(xf[t:t + 1] @ gate_up[e].float().t(), activation).to(self.dtype)
+          y = (h.float() @ down[e].float().t()).to(self.dtype).float()[0]
+        elif e < num_experts:
           h = self.gated_activation((xf[t:t + 1] @ gate_up[e].float().t()).to(self.dtype), activation)
           y = (h.float() @ down[e].float().t()).to(self.dtype).float()[0]
         else:
@@ -419,6 +446,162 @@ class ReferenceOps:
     for x, w in zip(branches, scales):
       total = total + self._rms(x, w, eps, False)
     return (total / len(branches)).to(self.dtype)
+
+  # ---- a stream kept several times ---------------------------------------------------
+  def spread_streams(self, h, copies):
+    return h[:, None, :].repeat(1, copies, 1).contiguous()
+
+  def streams_step(self, lanes, branch, mix, out, weights, norm_weight, eps, plus_one, rows):
+    """lanes [T, S, W] float32.  With `branch`: lanes[:, t] <- sum_s mix[s, t] lanes[:, s] + out[t] *
+    branch (in place; with `rows` only those rows are computed and nothing is written).  With
+    `weights`: returns rms(sum_s weights[s] lanes[:, s]) * norm_weight in the activation dtype
+    (`norm_weight` None: the sum itself, float32)."""
+    x = lanes if rows is None else lanes[rows.long()]
+    if branch is not None:
+      y = branch.float() if rows is None else branch[rows.long()].float()
+      x = torch.einsum("sr,tsw->trw", mix.float(), x) + out.float()[None, :, None] * y[:, None, :]
+      if rows is None:
+        lanes.copy_(x)
+    if weights is None:
+      return None
+    u = torch.einsum("s,tsw->tw", weights.float(), x)
+    if norm_weight is None:
+      return u
+    return self._rms(u, norm_weight, eps, plus_one).to(self.dtype)
+
+  # ---- short convolutions with their state ------------------------------------------------
+  def short_conv(self, x, weight, bias, state, ctx, *, activation=0, residual=False, offset=0, channels=None,
+                 out_dtype=None):
+    """Causal convolution over time per channel on x[:, offset : offset + channels]: y_t = sum_j
+    weight[:, j] * x_(t - K + 1 + j) (+ bias), the K - 1 inputs before a step's first token read from
+    `state` [slots, K - 1, channels] (float32), which then takes the step's last inputs.  activation 1:
+    silu.  residual: x + y."""
+    channels = x.shape[1] - offset if channels is None else channels
+    xs = x[:, offset:offset + channels].float()
+    taps = weight.shape[1]
+    y = torch.empty_like(xs)
+    for b in range(ctx.num_seqs):
+      r0, r1 = int(ctx.host["cu_q"][b]), int(ctx.host["cu_q"][b + 1])
+      n = r1 - r0
+      if taps > 1:
+        slot = int(ctx.host["slots"][b])
+        seen = torch.cat([state[slot].float(), xs[r0:r1]], dim=0)
+        state[slot] = seen[-(taps - 1):]
+      else:
+        seen = xs[r0:r1]
+      y[r0:r1] = sum(seen[j:j + n] * weight[:, j].float()[None, :] for j in range(taps))
+    if bias is not None:
+      y = y + bias.float()[None, :]
+    if activation == 1:
+      y = y * torch.sigmoid(y)
+    if residual:
+      y = xs + y
+    return y.to(out_dtype or self.dtype)
+
+  # ---- attention over latents -----------------------------------------------------------
+  @staticmethod
+  def _turn_part(x, positions, freq):
+    """Dims i and i + n of the first 2n dims of x [T, ..., D] turn by positions * freq[i]."""
+    if freq is None:
+      return x
+    n = freq.numel()
+    angle = positions.float()[:, None] * freq.float()[None, :]
+    while angle.dim() < x.dim():
+      angle = angle[:, None]
+    c, s = torch.cos(angle), torch.sin(angle)
+    a, b = x[..., :n], x[..., n:2 * n]
+    return torch.cat([a * c - b * s, b * c + a * s, x[..., 2 * n:]], dim=-1)
+
+  def latent_prepare(self, down, query_norm, kv_norm, eps, freq, *, query_rank, kv_rank, rotated_dim, storage,
+                     block_table, ctx):
+    d = down.float()
+    cq = self._rms(d[:, :query_rank], query_norm, eps, False)
+    c = self._rms(d[:, query_rank:query_rank + kv_rank], kv_norm, eps, False)
+    kr = self._turn_part(d[:, query_rank + kv_rank:query_rank + kv_rank + rotated_dim], ctx.positions, freq)
+    if storage is not None:
+      ps = ctx.page_size
+      pos = ctx.positions.long()
+      page = block_table[ctx.token_seq.long(), pos // ps].long()
+      assert (page >= 0).all(), "a token would be written to a page the request does not hold"
+      rows = storage.view(storage.shape[0], ps, kv_rank + rotated_dim)
+      rows[page, pos % ps] = torch.cat([c, kr], dim=1).to(storage.dtype)
+    return cq.to(self.dtype)
+
+  def latent_queries(self, q, key_up_t, freq, scale, ctx, *, num_heads, head_dim, rotated_dim):
+    t = q.shape[0]
+    qh = q.float().reshape(t, num_heads, head_dim + rotated_dim)
+    plain = torch.einsum("thd,hrd->thr", qh[..., :head_dim], key_up_t.float())
+    turned = self._turn_part(qh[..., head_dim:], ctx.positions, freq)
+    return (torch.cat([plain, turned], dim=-1) * scale).reshape(t, -1).to(self.dtype)
+
+  def head_linear(self, x, w):
+    """x [T, H * Din] . w [H, Dout, Din]^T per head -> [T, H * Dout]."""
+    h, dout, din = w.shape
+    y = torch.einsum("thd,hod->tho", x.float().reshape(x.shape[0], h, din), w.float())
+    return y.reshape(x.shape[0], h * dout).to(self.dtype)
+
+  # ---- the generalized delta rule ---------------------------------------------------------
+  def tanh_columns(self, x, offset, n):
+    return torch.tanh(x[:, offset:offset + n].float()).to(self.dtype)
+
+  def general_delta_scan(self, pre, low, decay_bias, removal_bias, state, ctx, *, num_heads, head_dim):
+    t = pre.shape[0]
+    inner = num_heads * head_dim
+    shape = (t, num_heads, head_dim)
+    r, k, v = (pre[:, i * inner:(i + 1) * inner].float().reshape(shape) for i in range(3))
+    take = torch.sigmoid(pre[:, 4 * inner:5 * inner].float() + removal_bias).reshape(shape)
+    decay = torch.exp(-math.exp(-0.5) * torch.sigmoid(low[:, :inner].float() + decay_bias)).reshape(shape)
+    unit = k / torch.sqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+    out = torch.empty(shape, dtype=torch.float32, device=pre.device)
+    for b in range(ctx.num_seqs):
+      r0, r1 = int(ctx.host["cu_q"][b]), int(ctx.host["cu_q"][b + 1])
+      slot = int(ctx.host["slots"][b])
+      s = state[slot].clone()  # [H, dk, dv]
+      for i in range(r0, r1):
+        seen = torch.einsum("hk,hkv->hv", unit[i], s)
+        s = (decay[i][:, :, None] * s - (take[i] * unit[i])[:, :, None] * seen[:, None, :]
+             + k[i][:, :, None] * v[i][:, None, :])
+        out[i] = torch.einsum("hkv,hk->hv", s, r[i])
+      state[slot] = s
+    return out
+
+  def group_norm_gate(self, o, weight, eps, *, groups, gate=None, gate_offset=0, gate_kind="none"):
+    """o float32 [T, ...] of N numbers per token, RMS-normed in `groups` equal parts, times weight [N];
+    the gate gate[:, gate_offset : gate_offset + N] acts as silu before the norm or as sigmoid after it."""
+    t = o.shape[0]
+    y = o.reshape(t, -1).float()
+    n = y.shape[1]
+    g = gate[:, gate_offset:gate_offset + n].float() if gate is not None and gate_kind != "none" else None
+    if gate_kind == "silu_before":
+      y = y * g * torch.sigmoid(g)
+    y = y.reshape(t, groups, n // groups)
+    y = (y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps)).reshape(t, n) * weight.float()[None, :]
+    if gate_kind == "sigmoid_after":
+      y = y * torch.sigmoid(g)
+    return y.to(self.dtype)
+
+  # ---- the state-space recurrence ---------------------------------------------------------
+  def state_space_scan(self, xbc, pre, step_offset, step_bias, neg_rate, skip, state, ctx, *, num_heads, value_dim,
+                       state_dim, num_groups):
+    t = xbc.shape[0]
+    inner, gn = num_heads * value_dim, num_groups * state_dim
+    x = xbc[:, :inner].float().reshape(t, num_heads, value_dim)
+    per = num_heads // num_groups
+    bm = xbc[:, inner:inner + gn].float().reshape(t, num_groups, state_dim).repeat_interleave(per, dim=1)
+    cm = xbc[:, inner + gn:inner + 2 * gn].float().reshape(t, num_groups, state_dim).repeat_interleave(per, dim=1)
+    dt = torch.nn.functional.softplus(pre[:, step_offset:step_offset + num_heads].float() + step_bias[None, :],
+                                      threshold=1e9)
+    decay = torch.exp(neg_rate[None, :] * dt)
+    out = torch.empty(t, num_heads, value_dim, dtype=torch.float32, device=xbc.device)
+    for b in range(ctx.num_seqs):
+      r0, r1 = int(ctx.host["cu_q"][b]), int(ctx.host["cu_q"][b + 1])
+      slot = int(ctx.host["slots"][b])
+      s = state[slot].clone()  # [H, N, dv]
+      for i in range(r0, r1):
+        s = decay[i][:, None, None] * s + (dt[i][:, None] * bm[i])[:, :, None] * x[i][:, None, :]
+        out[i] = torch.einsum("hnv,hn->hv", s, cm[i]) + skip[:, None] * x[i]
+      state[slot] = s
+    return out
 
   # ---- sampling -------------------------------------------------------------
   def token_logprobs(self, logits, tokens, temperature, top_k, top_p):
