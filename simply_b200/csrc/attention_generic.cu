@@ -16,7 +16,10 @@
 // window W and blocks of P tokens, position i also sees, ahead of its window and under the same
 // softmax, one key and value per block c with c*P + P - 1 <= i - W, read from a second paged
 // storage that holds one entry per P tokens in the page of the block's first token.  Blocks
-// are visited in tiles of 32 by block number, before the tokens.
+// are visited in tiles of 32 by block number, before the tokens.  `tied`: an entry has one row of
+// head_dim numbers whose first v_dim are its value as well (a cache of latents; a page then holds
+// key rows only).  `sink`: one learned number per query head whose exponential joins the softmax's
+// denominator; it has no key and no value.
 //
 // This is the true 32-bit path's attention and the fallback of the bfloat16
 // path for shapes its tensor-core kernels refuse.
@@ -116,7 +119,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
                                T* __restrict__ out, int num_tokens, int num_q_heads, int num_kv_heads,
                                int head_dim, int v_dim, int page_size, int num_pages, float cap, int window,
                                const T* __restrict__ pool, const int* __restrict__ pool_table,
-                               int pool_max_pages, int pool_len, int pool_pages, int* err) {
+                               int pool_max_pages, int pool_len, int pool_pages, int tied,
+                               const float* __restrict__ sink, int* err) {
   pdl_wait_block();
   pdl_launch_dependents();
   // head_dim floats of q, then per warp its running maximum, sum and v_dim partial results
@@ -162,7 +166,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
     }
   }
 
-  const size_t page_stride = (size_t)num_kv_heads * page_size * (head_dim + v_dim);
+  const size_t page_stride = (size_t)num_kv_heads * page_size * (tied ? head_dim : head_dim + v_dim);
   const size_t value_base = (size_t)num_kv_heads * page_size * head_dim;
   for (int tile = (lo / 32) * 32; tile <= pos; tile += 32) {
     if (((tile >> 5) & (GEN_WARPS - 1)) != warp) continue;  // by the tile's absolute number
@@ -176,7 +180,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
       } else {
         const size_t row = (size_t)m * page_size + j % page_size;
         kr = cache + page * page_stride + row * head_dim;
-        vr = cache + page * page_stride + value_base + row * v_dim;
+        vr = tied ? kr : cache + page * page_stride + value_base + row * v_dim;
       }
     }
     gen_tile<T>(kr, vr, qs, head_dim, v_dim, cap, lane, m_run, l_run, acc);
@@ -197,12 +201,14 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
   float m_all = part[0];
 #pragma unroll
   for (int w = 1; w < GEN_WARPS; ++w) m_all = fmaxf(m_all, part[(size_t)w * (v_dim + 2)]);
+  if (sink != nullptr) m_all = fmaxf(m_all, sink[n]);
   float scale[GEN_WARPS], l_all = 0.f;
 #pragma unroll
   for (int w = 0; w < GEN_WARPS; ++w) {
     scale[w] = expf(part[(size_t)w * (v_dim + 2)] - m_all);
     l_all += part[(size_t)w * (v_dim + 2) + 1] * scale[w];
   }
+  if (sink != nullptr) l_all += expf(sink[n] - m_all);
   T* op = out + ((size_t)t * num_q_heads + n) * v_dim;
   const float inv = 1.0f / l_all;
   for (int d = lane; d < v_dim; d += 32) {
@@ -218,9 +224,10 @@ extern "C" int sb_paged_attention_general(const void* q, int dtype, const void* 
                                           void* out, int num_tokens, int num_q_heads, int num_kv_heads,
                                           int head_dim, int v_dim, int page_size, int num_pages, float cap,
                                           int window, const void* pool, const int* pool_table,
-                                          int pool_max_pages, int pool_len, int pool_pages, int* err,
-                                          cudaStream_t stream) {
+                                          int pool_max_pages, int pool_len, int pool_pages, int tied,
+                                          const float* sink, int* err, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
+  if (tied && (pool != nullptr || v_dim > head_dim)) return -13;
   if (head_dim <= 0 || head_dim > 32 * GEN_MAX_DPL || v_dim <= 0 || v_dim > 32 * GEN_MAX_DPL) return -7;
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads) return -8;
   const long long items = (long long)num_tokens * num_q_heads;
@@ -231,12 +238,12 @@ extern "C" int sb_paged_attention_general(const void* q, int dtype, const void* 
     sb_launch(paged_attention_generic_kernel<float>, blocks, GEN_WARPS * 32, smem, stream, (const float*)q,
         (const float*)cache, block_table, max_pages, token_seq, positions, (float*)out, num_tokens,
         num_q_heads, num_kv_heads, head_dim, v_dim, page_size, num_pages, cap, window, (const float*)pool, pool_table,
-        pool_max_pages, pool_len, pool_pages, err);
+        pool_max_pages, pool_len, pool_pages, tied, sink, err);
   else
     sb_launch(paged_attention_generic_kernel<bf16>, blocks, GEN_WARPS * 32, smem, stream, (const bf16*)q,
         (const bf16*)cache, block_table, max_pages, token_seq, positions, (bf16*)out, num_tokens,
         num_q_heads, num_kv_heads, head_dim, v_dim, page_size, num_pages, cap, window, (const bf16*)pool, pool_table,
-        pool_max_pages, pool_len, pool_pages, err);
+        pool_max_pages, pool_len, pool_pages, tied, sink, err);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -248,5 +255,5 @@ extern "C" int sb_paged_attention_generic(const void* q, int dtype, const void* 
                                           int* err, cudaStream_t stream) {
   return sb_paged_attention_general(q, dtype, cache, block_table, max_pages, token_seq, positions, out, num_tokens,
                                     num_q_heads, num_kv_heads, head_dim, head_dim, page_size, num_pages, cap,
-                                    window, nullptr, nullptr, 0, 0, 0, err, stream);
+                                    window, nullptr, nullptr, 0, 0, 0, 0, nullptr, err, stream);
 }

@@ -465,28 +465,29 @@ extern "C" int sb_rotate_headnorm_store(const void* proj, int row_width, int dty
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
-sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ gate, int gate_width, int width) {
+sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ gate, int gate_width, int width, int per) {
   pdl_wait_block();
   pdl_launch_dependents();
   const int t = blockIdx.y;
   for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < width; c += gridDim.x * blockDim.x) {
-    const float g = to_f32<T>(gate[(size_t)t * gate_width + c]);
+    const float g = to_f32<T>(gate[(size_t)t * gate_width + c / per]);  // one gate per `per` neighbours
     const size_t at = (size_t)t * width + c;
     x[at] = from_f32<T>(to_f32<T>(x[at]) / (1.0f + expf(-g)));
   }
 }
 
 extern "C" int sb_sigmoid_gate(void* x, const void* gate, int gate_width, int dtype, int num_tokens, int width,
-                               cudaStream_t stream) {
+                               int per, cudaStream_t stream) {
   if (num_tokens == 0 || width == 0) return 0;
+  if (per < 1) return -13;
   for (int t0 = 0; t0 < num_tokens; t0 += 65535) {
     const dim3 grid((unsigned)min((width + 255) / 256, 64), (unsigned)min(65535, num_tokens - t0));
     if (dtype == SB_DTYPE_F32)
       sb_launch(sigmoid_gate_kernel<float>, grid, 256, 0, stream, (float*)x + (size_t)t0 * width,
-                (const float*)gate + (size_t)t0 * gate_width, gate_width, width);
+                (const float*)gate + (size_t)t0 * gate_width, gate_width, width, per);
     else
       sb_launch(sigmoid_gate_kernel<bf16>, grid, 256, 0, stream, (bf16*)x + (size_t)t0 * width,
-                (const bf16*)gate + (size_t)t0 * gate_width, gate_width, width);
+                (const bf16*)gate + (size_t)t0 * gate_width, gate_width, width, per);
   }
   SB_LAUNCH_CHECK();
   return 0;

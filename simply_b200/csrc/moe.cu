@@ -207,6 +207,7 @@ __device__ __forceinline__ float moe_activation(float g, int act) {
     return 0.5f * g * (1.0f + tanhf(c * (g + 0.044715f * g * g * g)));
   }
   if (act == 1) return g / (1.0f + expf(-g));
+  if (act == 4) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));  // the exact gelu
   return fmaxf(g, 0.f);
 }
 
@@ -419,18 +420,22 @@ moe_product_kernel(const T* __restrict__ A, const int* __restrict__ row_pair, in
     for (int idx = threadIdx.x; idx < rows * 2 * MOE_TILE_N; idx += blockDim.x) {
       const int r = idx / (2 * MOE_TILE_N), c = idx - r * 2 * MOE_TILE_N;
       const int s = c / MOE_TILE_N, cc = c - s * MOE_TILE_N;
-      if (n0 + c < N) out[(size_t)(row0 + r) * N + n0 + c] = from_f32<T>(Cs[(s * MOE_TILE_M + r) * CLD + cc]);
+      if (n0 + c < N) {
+        const float v = Cs[(s * MOE_TILE_M + r) * CLD + cc];
+        out[(size_t)(row0 + r) * N + n0 + c] = from_f32<T>(act >= 0 ? moe_activation(v, act) : v);
+      }
     }
   }
 }
 
 // gated = 1: W [E, 2 N, K] (gate rows, then up rows), out [P, N] = act(gate) * up;
-// gated = 0: W [E, N, K], out [P, N].
+// gated = 0: W [E, N, K], out [P, N] = act(sums), act -1: the sums themselves.
+// act: 0 gelu (tanh form), 1 silu, 2 relu, 4 the exact gelu.
 extern "C" int sb_moe_product(const void* A, const int* row_pair, int pair_div, const void* W, int dtype, int gated,
                               int K, int N, const int* tile_expert, const int* tile_row0, const int* tile_rows,
                               int max_tiles, int act, void* out, cudaStream_t stream) {
   if (max_tiles == 0 || N == 0) return 0;
-  if (K <= 0 || act < 0 || act > 2 || pair_div < 1) return -13;
+  if (K <= 0 || act < (gated ? 0 : -1) || act > 4 || act == 3 || pair_div < 1) return -13;
   const size_t stride = (size_t)(gated ? 2 : 1) * N * K;
   const int per_block = gated ? MOE_TILE_N : 2 * MOE_TILE_N;
   const dim3 grid(max_tiles, (N + per_block - 1) / per_block);

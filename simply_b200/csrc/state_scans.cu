@@ -1,0 +1,431 @@
+// Walks of two recurrent mixers whose state is a matrix per head and request (float32, in a state
+// slot): the generalized delta rule and the state-space recurrence of Mamba-2.
+//
+//   generalized delta rule   S [d, d] per head;  per token, with decay w, unit key u, removal rate a:
+//                              p   = u^T S                       (the old state)
+//                              S  <- diag(w) S - (a * u) p + k v^T
+//                              o   = S^T r
+//   state-space recurrence   S [N, dv] per head;  S <- exp(-exp(A) dt) S + dt B x^T;  y = S^T C + D x
+//
+// Both share one layout: a block owns `cols` columns of one (head, sequence) and walks the
+// sequence's tokens of this step in order; a column of S is held by RS neighbouring lanes with ROWS
+// rows each in registers (row rs + RS r), sums over rows are butterfly sums over those lanes in an
+// order that does not depend on the step's shape; the tokens' vectors come to shared memory by
+// cp.async, a chunk of tokens at a time, the next chunk under way while this one is walked.  The
+// state is read once and written once per step, by the first row of its slot (a decode graph pads
+// its batch by repeating a request).  Everything is float32.
+#include "common.cuh"
+
+#define SB_ERR_BAD_SLOT 16
+
+__device__ __forceinline__ bool owns_slot(const int* slots, int b) {
+  const int slot = slots[b];
+  for (int i = 0; i < b; ++i)
+    if (slots[i] == slot) return false;
+  return true;
+}
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+__device__ __forceinline__ void stage4(float* smem, const float* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void stage16(float* smem, const float* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+// n floats; `wide`: both addresses are 16-byte aligned and n is a multiple of 4.
+__device__ __forceinline__ void stage_row(float* smem, const float* gmem, int n, bool wide) {
+  if (wide) {
+    for (int c = threadIdx.x * 4; c < n; c += blockDim.x * 4) stage16(smem + c, gmem + c);
+  } else {
+    for (int c = threadIdx.x; c < n; c += blockDim.x) stage4(smem + c, gmem + c);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Inputs of the generalized delta rule, once per token.  pre [T, pre_width] = r | k | v | gate | a | ...
+// (each H d), low [T, low_width] = the decay's low-rank output (H d).  A warp per (token, head):
+//   vecs [T, H, 5, d] = w, u, a * u, k, r ;  vals [T, H, d] = v ;  dots [T, H, 2] = r . (a u), r . k
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+general_delta_inputs_kernel(const T* __restrict__ pre, int pre_width, const T* __restrict__ low, int low_width,
+                            const float* __restrict__ decay_bias, const float* __restrict__ removal_bias, int H,
+                            int d, int num_tokens, float* __restrict__ vecs, float* __restrict__ vals,
+                            float* __restrict__ dots) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)num_tokens * H) return;
+  const int t = (int)(item / H), h = (int)(item - (long long)t * H);
+  const int inner = H * d;
+  const T* row = pre + (size_t)t * pre_width + (size_t)h * d;
+  const T* lrow = low + (size_t)t * low_width + (size_t)h * d;
+  float kk = 0.f;
+  for (int c = lane; c < d; c += 32) {
+    const float k = to_f32<T>(row[inner + c]);
+    kk = fmaf(k, k, kk);
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(kk) + 1e-6f);
+  const float rate = 0.6065306597126334f;  // e^(-1/2)
+  float* out = vecs + (size_t)item * 5 * d;
+  float ra = 0.f, rk = 0.f;
+  for (int c = lane; c < d; c += 32) {
+    const float r = to_f32<T>(row[c]), k = to_f32<T>(row[inner + c]);
+    const float a = sigmoidf_(to_f32<T>(row[4 * inner + c]) + removal_bias[h * d + c]);
+    const float w = expf(-rate * sigmoidf_(to_f32<T>(lrow[c]) + decay_bias[h * d + c]));
+    const float u = k * inv, au = a * u;
+    out[c] = w;
+    out[d + c] = u;
+    out[2 * d + c] = au;
+    out[3 * d + c] = k;
+    out[4 * d + c] = r;
+    vals[(size_t)item * d + c] = to_f32<T>(row[2 * inner + c]);
+    ra = fmaf(r, au, ra);
+    rk = fmaf(r, k, rk);
+  }
+  ra = warp_sum(ra);
+  rk = warp_sum(rk);
+  if (lane == 0) {
+    dots[(size_t)item * 2] = ra;
+    dots[(size_t)item * 2 + 1] = rk;
+  }
+}
+
+template <int RS, int ROWS>
+__global__ void __launch_bounds__(128)
+general_delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ vals,
+                          const float* __restrict__ dots, float* __restrict__ state, const int* __restrict__ cu_q,
+                          const int* __restrict__ slots, int num_slots, int H, int d, int cols, int chunk,
+                          float* __restrict__ out, int* err) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) float stage[];  // two buffers of chunk x (5 d | cols_pad | 4)
+  const int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * cols;
+  const int rs = threadIdx.x % RS, col_local = threadIdx.x / RS;
+  const int col = col0 + col_local;
+  const bool on = col_local < cols && col < d;
+  const int first = cu_q[b], n = cu_q[b + 1] - first;
+  const int slot = slots[b];
+  if (slot < 0 || slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_SLOT);
+    return;
+  }
+  const int cols_pad = (cols + 3) & ~3;
+  const int per_token = 5 * d + cols_pad + 4;
+  const bool wide = (d & 3) == 0;
+
+  auto issue = [&](int which, int base) {
+    float* buf = stage + (size_t)which * chunk * per_token;
+    const int count = min(chunk, n - base);
+    for (int i = 0; i < count; ++i) {
+      const size_t at = (size_t)(first + base + i) * H + h;
+      float* dst = buf + (size_t)i * per_token;
+      stage_row(dst, vecs + at * 5 * d, 5 * d, wide);
+      for (int c = threadIdx.x; c < cols; c += blockDim.x) stage4(dst + 5 * d + c, vals + at * d + min(col0 + c, d - 1));
+      if (threadIdx.x < 2) stage4(dst + 5 * d + cols_pad + threadIdx.x, dots + at * 2 + threadIdx.x);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+
+  if (n > 0) issue(0, 0);
+  float* S = state + ((size_t)slot * H + h) * d * d;
+  float s[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const int row = rs + RS * r;
+    s[r] = (on && row < d) ? S[(size_t)row * d + col] : 0.f;
+  }
+  int which = 0;
+  for (int base = 0; base < n; base += chunk, which ^= 1) {
+    const int count = min(chunk, n - base);
+    if (base + chunk < n) {
+      issue(which ^ 1, base + chunk);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
+    __syncthreads();
+    const float* buf = stage + (size_t)which * chunk * per_token;
+    for (int i = 0; i < count; ++i) {
+      const float* w = buf + (size_t)i * per_token;
+      const float* u = w + d;
+      const float* au = w + 2 * d;
+      const float* k = w + 3 * d;
+      const float* rr = w + 4 * d;
+      const float vj = w[5 * d + min(col_local, cols - 1)];
+      const float ra = w[5 * d + cols_pad], rk = w[5 * d + cols_pad + 1];
+      // One pass over the old state gives both sums: o = r . (w * s) - p (r . a u) + v_j (r . k).
+      float p = 0.f, od = 0.f;
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const int row = rs + RS * r;
+        if (row < d) {
+          p = fmaf(u[row], s[r], p);
+          s[r] *= w[row];
+          od = fmaf(rr[row], s[r], od);
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < RS; o <<= 1) {
+        p += __shfl_xor_sync(0xffffffffu, p, o);
+        od += __shfl_xor_sync(0xffffffffu, od, o);
+      }
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const int row = rs + RS * r;
+        if (row < d) s[r] = fmaf(k[row], vj, fmaf(-au[row], p, s[r]));
+      }
+      if (on && rs == 0) out[((size_t)(first + base + i) * H + h) * d + col] = fmaf(vj, rk, fmaf(-p, ra, od));
+    }
+    __syncthreads();  // the buffer is filled again two chunks on
+  }
+  if (on && owns_slot(slots, b)) {
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int row = rs + RS * r;
+      if (row < d) S[(size_t)row * d + col] = s[r];
+    }
+  }
+}
+
+// scratch: float32 [T, H, 6 d + 2].
+extern "C" int sb_general_delta_scan(const void* pre, int pre_width, const void* low, int low_width, int dtype,
+                                     const float* decay_bias, const float* removal_bias, float* state,
+                                     const int* cu_q, const int* slots, int num_tokens, int num_seqs, int num_slots,
+                                     int H, int d, int max_q_len, float* scratch, float* out, int* err,
+                                     cudaStream_t stream) {
+  if (num_seqs == 0 || num_tokens == 0) return 0;
+  if (d <= 0 || d > 1024 || H <= 0) return -13;
+  float* vecs = scratch;
+  float* vals = vecs + (size_t)num_tokens * H * 5 * d;
+  float* dots = vals + (size_t)num_tokens * H * d;
+  const long long items = (long long)num_tokens * H;
+  const unsigned in_blocks = (unsigned)((items + 7) / 8);
+  if (dtype == SB_DTYPE_F32)
+    sb_launch(general_delta_inputs_kernel<float>, in_blocks, 256, 0, stream, (const float*)pre, pre_width,
+              (const float*)low, low_width, decay_bias, removal_bias, H, d, num_tokens, vecs, vals, dots);
+  else
+    sb_launch(general_delta_inputs_kernel<bf16>, in_blocks, 256, 0, stream, (const bf16*)pre, pre_width,
+              (const bf16*)low, low_width, decay_bias, removal_bias, H, d, num_tokens, vecs, vals, dots);
+  SB_LAUNCH_CHECK();
+  const int rows = d <= 256 ? 8 : 32;
+  int rs = 1;
+  while (rs * rows < d) rs <<= 1;
+  const bool long_walk = max_q_len >= 64;
+  const int threads = long_walk ? 128 : 64;
+  int chunk = 1;
+  while (chunk < 16 && chunk < max_q_len) chunk <<= 1;
+  if ((size_t)2 * chunk * (5 * d + 40) * sizeof(float) > 160 * 1024) chunk = chunk > 4 ? 4 : chunk;
+  int cols = threads / rs;
+  if (cols < 1) cols = 1;
+  if (cols > d) cols = d;
+  const int block = ((cols * rs + 31) / 32) * 32;
+  const dim3 grid(H, num_seqs, (d + cols - 1) / cols);
+  const size_t smem = (size_t)2 * chunk * (5 * d + ((cols + 3) & ~3) + 4) * sizeof(float);
+  if (smem > 200 * 1024) return -13;
+#define SB_GD_SCAN(RS_, ROWS_)                                                                                  \
+  do {                                                                                                          \
+    if (smem > 48 * 1024)                                                                                       \
+      cudaFuncSetAttribute(general_delta_scan_kernel<RS_, ROWS_>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                           (int)smem);                                                                          \
+    if (long_walk)                                                                                              \
+      sb_launch_plain(general_delta_scan_kernel<RS_, ROWS_>, grid, block, smem, stream, vecs, vals, dots, state, \
+                      cu_q, slots, num_slots, H, d, cols, chunk, out, err);                                     \
+    else                                                                                                        \
+      sb_launch(general_delta_scan_kernel<RS_, ROWS_>, grid, block, smem, stream, vecs, vals, dots, state,     \
+                cu_q, slots, num_slots, H, d, cols, chunk, out, err);                                           \
+  } while (0)
+#define SB_GD(RS_)                               \
+  do {                                           \
+    if (rows == 8) SB_GD_SCAN(RS_, 8);           \
+    else SB_GD_SCAN(RS_, 32);                    \
+  } while (0)
+  switch (rs) {
+    case 1: SB_GD(1); break;
+    case 2: SB_GD(2); break;
+    case 4: SB_GD(4); break;
+    case 8: SB_GD(8); break;
+    case 16: SB_GD(16); break;
+    default: SB_GD(32); break;
+  }
+#undef SB_GD
+#undef SB_GD_SCAN
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// The state-space recurrence.  xbc [T, C] float32 = x (H dv) | B (G N) | C (G N) after the
+// convolution and silu; steps [T, H, 2] = exp(neg_rate dt), dt with dt = softplus(pre + bias).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void state_space_steps_kernel(const T* __restrict__ pre, int pre_width, int offset,
+                                         const float* __restrict__ step_bias, const float* __restrict__ neg_rate,
+                                         int H, long long total, float* __restrict__ steps) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / H;
+  const int h = (int)(i - t * H);
+  const float z = to_f32<T>(pre[t * pre_width + offset + h]) + step_bias[h];
+  const float dt = z > 20.f ? z : log1pf(expf(z));
+  steps[2 * i] = expf(neg_rate[h] * dt);
+  steps[2 * i + 1] = dt;
+}
+
+template <int RS, int ROWS>
+__global__ void __launch_bounds__(128)
+state_space_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ steps,
+                        const float* __restrict__ skip, float* __restrict__ state, const int* __restrict__ cu_q,
+                        const int* __restrict__ slots, int num_slots, int H, int G, int N, int dv, int cols,
+                        int chunk, float* __restrict__ out, int* err) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) float stage[];  // two buffers of chunk x (B: N | C: N | x: cols_pad | 4)
+  const int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * cols;
+  const int rs = threadIdx.x % RS, col_local = threadIdx.x / RS;
+  const int col = col0 + col_local;
+  const bool on = col_local < cols && col < dv;
+  const int first = cu_q[b], n = cu_q[b + 1] - first;
+  const int slot = slots[b];
+  if (slot < 0 || slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_SLOT);
+    return;
+  }
+  const int g = h / (H / G);
+  const int inner = H * dv;
+  const int cols_pad = (cols + 3) & ~3;
+  const int n_pad = (N + 3) & ~3;
+  const int per_token = 2 * n_pad + cols_pad + 4;
+  const bool wide = (N & 3) == 0 && (C & 3) == 0 && (inner & 3) == 0;
+  const float d_skip = skip[h];
+
+  auto issue = [&](int which, int base) {
+    float* buf = stage + (size_t)which * chunk * per_token;
+    const int count = min(chunk, n - base);
+    for (int i = 0; i < count; ++i) {
+      const float* row = xbc + (size_t)(first + base + i) * C;
+      float* dst = buf + (size_t)i * per_token;
+      stage_row(dst, row + inner + (size_t)g * N, N, wide);
+      stage_row(dst + n_pad, row + inner + (size_t)(G + g) * N, N, wide);
+      for (int c = threadIdx.x; c < cols; c += blockDim.x)
+        stage4(dst + 2 * n_pad + c, row + (size_t)h * dv + min(col0 + c, dv - 1));
+      if (threadIdx.x < 2)
+        stage4(dst + 2 * n_pad + cols_pad + threadIdx.x, steps + ((size_t)(first + base + i) * H + h) * 2 + threadIdx.x);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+
+  if (n > 0) issue(0, 0);
+  float* S = state + ((size_t)slot * H + h) * N * dv;
+  float s[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const int row = rs + RS * r;
+    s[r] = (on && row < N) ? S[(size_t)row * dv + col] : 0.f;
+  }
+  int which = 0;
+  for (int base = 0; base < n; base += chunk, which ^= 1) {
+    const int count = min(chunk, n - base);
+    if (base + chunk < n) {
+      issue(which ^ 1, base + chunk);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
+    __syncthreads();
+    const float* buf = stage + (size_t)which * chunk * per_token;
+    for (int i = 0; i < count; ++i) {
+      const float* bm = buf + (size_t)i * per_token;
+      const float* cm = bm + n_pad;
+      const float xj = bm[2 * n_pad + min(col_local, cols - 1)];
+      const float decay = bm[2 * n_pad + cols_pad], dt = bm[2 * n_pad + cols_pad + 1];
+      const float push = dt * xj;
+      float y = 0.f;
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const int row = rs + RS * r;
+        if (row < N) {
+          s[r] = fmaf(push, bm[row], decay * s[r]);
+          y = fmaf(s[r], cm[row], y);
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < RS; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+      if (on && rs == 0) out[((size_t)(first + base + i) * H + h) * dv + col] = fmaf(d_skip, xj, y);
+    }
+    __syncthreads();
+  }
+  if (on && owns_slot(slots, b)) {
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int row = rs + RS * r;
+      if (row < N) S[(size_t)row * dv + col] = s[r];
+    }
+  }
+}
+
+// scratch: float32 [T, H, 2].
+extern "C" int sb_state_space_scan(const float* xbc, int C, const void* pre, int pre_width, int dtype,
+                                   int step_offset, const float* step_bias, const float* neg_rate,
+                                   const float* skip, float* state, const int* cu_q, const int* slots,
+                                   int num_tokens, int num_seqs, int num_slots, int H, int G, int N, int dv,
+                                   int max_q_len, float* scratch, float* out, int* err, cudaStream_t stream) {
+  if (num_seqs == 0 || num_tokens == 0) return 0;
+  if (N <= 0 || N > 1024 || dv <= 0 || H <= 0 || G <= 0 || H % G) return -13;
+  const long long total = (long long)num_tokens * H;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == SB_DTYPE_F32)
+    sb_launch(state_space_steps_kernel<float>, blocks, 256, 0, stream, (const float*)pre, pre_width, step_offset,
+              step_bias, neg_rate, H, total, scratch);
+  else
+    sb_launch(state_space_steps_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)pre, pre_width, step_offset,
+              step_bias, neg_rate, H, total, scratch);
+  SB_LAUNCH_CHECK();
+  const int rows = N <= 256 ? 8 : 32;
+  int rs = 1;
+  while (rs * rows < N) rs <<= 1;
+  const bool long_walk = max_q_len >= 64;
+  const int threads = long_walk ? 128 : 64;
+  int chunk = 1;
+  while (chunk < 16 && chunk < max_q_len) chunk <<= 1;
+  int cols = threads / rs;
+  if (cols < 1) cols = 1;
+  if (cols > dv) cols = dv;
+  const int block = ((cols * rs + 31) / 32) * 32;
+  const dim3 grid(H, num_seqs, (dv + cols - 1) / cols);
+  const size_t smem = (size_t)2 * chunk * (2 * ((N + 3) & ~3) + ((cols + 3) & ~3) + 4) * sizeof(float);
+  if (smem > 200 * 1024) return -13;
+#define SB_SS_SCAN(RS_, ROWS_)                                                                                 \
+  do {                                                                                                         \
+    if (smem > 48 * 1024)                                                                                      \
+      cudaFuncSetAttribute(state_space_scan_kernel<RS_, ROWS_>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                           (int)smem);                                                                         \
+    if (long_walk)                                                                                             \
+      sb_launch_plain(state_space_scan_kernel<RS_, ROWS_>, grid, block, smem, stream, xbc, C, scratch, skip,   \
+                      state, cu_q, slots, num_slots, H, G, N, dv, cols, chunk, out, err);                      \
+    else                                                                                                       \
+      sb_launch(state_space_scan_kernel<RS_, ROWS_>, grid, block, smem, stream, xbc, C, scratch, skip, state,  \
+                cu_q, slots, num_slots, H, G, N, dv, cols, chunk, out, err);                                   \
+  } while (0)
+#define SB_SS(RS_)                               \
+  do {                                           \
+    if (rows == 8) SB_SS_SCAN(RS_, 8);           \
+    else SB_SS_SCAN(RS_, 32);                    \
+  } while (0)
+  switch (rs) {
+    case 1: SB_SS(1); break;
+    case 2: SB_SS(2); break;
+    case 4: SB_SS(4); break;
+    case 8: SB_SS(8); break;
+    case 16: SB_SS(16); break;
+    default: SB_SS(32); break;
+  }
+#undef SB_SS
+#undef SB_SS_SCAN
+  SB_LAUNCH_CHECK();
+  return 0;
+}

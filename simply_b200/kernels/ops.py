@@ -249,7 +249,7 @@ class CudaOps:
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_paged_attention_general": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void,
-                                       c_int, c_int, c_int, c_void, c_void],
+                                       c_int, c_int, c_int, c_int, c_void, c_void, c_void],
         "sb_qk_norm_rotate_store": [c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_void, c_int, c_void,
                                     c_void, c_void, c_void, c_int, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_int, c_void, c_void],
@@ -268,7 +268,29 @@ class CudaOps:
         "sb_rotate_headnorm_store": [c_void, c_int, c_int, c_float, c_float, c_void, c_int, c_int, c_int, c_int,
                                      c_void, c_void, c_void, c_int, c_void, c_void, c_int, c_int, c_int, c_int,
                                      c_int, c_int, c_int, c_int, c_void, c_void],
-        "sb_sigmoid_gate": [c_void, c_void, c_int, c_int, c_int, c_int, c_void],
+        "sb_sigmoid_gate": [c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_void],
+        "sb_embed_positions": [c_void, c_void, c_int, c_void, c_void, c_float, c_void, c_int, c_int, c_int, c_int,
+                               c_void, c_void],
+        "sb_spread_streams": [c_void, c_void, c_int, c_int, c_int, c_void],
+        "sb_streams_step": [c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_int, c_float, c_int, c_void,
+                            c_int, c_void, c_void, c_int, c_int, c_int, c_void, c_void],
+        "sb_short_conv": [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int,
+                          c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void],
+        "sb_group_norm_gate": [c_void, c_void, c_int, c_int, c_int, c_int, c_void, c_float, c_int, c_int, c_int,
+                               c_void, c_void],
+        "sb_tanh_columns": [c_void, c_int, c_int, c_int, c_int, c_void, c_int, c_void],
+        "sb_table_route": [c_void, c_void, c_int, c_int, c_int, c_void, c_void, c_int, c_void, c_void],
+        "sb_head_linear": [c_void, c_int, c_int, c_int, c_void, c_int, c_int, c_int, c_int, c_void, c_int, c_int,
+                           c_float, c_int, c_void],
+        "sb_latent_prepare": [c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_int, c_int, c_int, c_int,
+                              c_void, c_void, c_void, c_int, c_int, c_int, c_void, c_void, c_int, c_void, c_void],
+        "sb_turn_query_part": [c_void, c_int, c_int, c_void, c_int, c_int, c_int, c_void, c_int, c_int, c_float,
+                               c_void, c_int, c_int, c_void],
+        "sb_general_delta_scan": [c_void, c_int, c_void, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_int,
+                                  c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void],
+        "sb_state_space_scan": [c_void, c_int, c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void,
+                                c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void,
+                                c_void, c_void],
         "sb_forget_scan": [c_void, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_void, c_void, c_void, c_void],
         "sb_moe_route": [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_int, c_int, c_float, c_int, c_int,
@@ -583,7 +605,18 @@ class CudaOps:
     return plan
 
   # ---- dense ----------------------------------------------------------------
-  def embed(self, table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.Tensor:
+  def embed(self, table: torch.Tensor, ids: torch.Tensor, scale: float, positions: torch.Tensor | None = None,
+            position_table: torch.Tensor | None = None, round_scale: bool = True) -> torch.Tensor:
+    """float32 rows table[id] * scale (+ position_table[position]).  `round_scale`: the factor is
+    rounded to the table's dtype first."""
+    if position_table is not None or not round_scale:
+      if position_table is not None and position_table.dtype != table.dtype:
+        raise KernelError("the embedding table and the position table must share one dtype")
+      out = self._new(ids.numel(), table.shape[1], dtype=torch.float32)
+      self._call("sb_embed_positions", _ptr(table), _ptr(position_table), _code(table), _ptr(ids), _ptr(positions),
+                 float(scale), _ptr(out), ids.numel(), table.shape[1], table.shape[0],
+                 position_table.shape[0] if position_table is not None else 0, _ptr(self.err))
+      return out
     if table.dtype == torch.bfloat16:
       # The reference rounds the constant to the activation dtype (simply/utils/module.py:477-481).
       rounded = self._rounded_scales.get(scale)
@@ -814,15 +847,20 @@ class CudaOps:
   # ---- attention ------------------------------------------------------------
   def paged_attention(self, q: torch.Tensor, storage: torch.Tensor, block_table: torch.Tensor, ctx: Any, *,
                       num_heads: int, num_kv_heads: int, head_dim: int, logit_softcap: float,
-                      window: int | None, value_dim: int | None = None, pooled: tuple | None = None) -> torch.Tensor:
+                      window: int | None, value_dim: int | None = None, pooled: tuple | None = None,
+                      values_in_keys: bool = False, sink: torch.Tensor | None = None) -> torch.Tensor:
     """`value_dim`: size of a value head where it is not the key heads'.  `pooled`: (storage of block
     entries, its block table, block length): with a window, one key and value per whole block that
-    has left the window, under the same softmax (csrc/attention_generic.cu)."""
+    has left the window, under the same softmax.  `values_in_keys`: an entry's value is the first
+    `value_dim` numbers of its key row (a cache of latents).  `sink`: float32 [heads], a number per
+    head whose exponential joins the softmax's denominator (csrc/attention_generic.cu)."""
     t = q.shape[0]
     value_dim = head_dim if value_dim is None else value_dim
     out = self._new(t, num_heads * value_dim, dtype=q.dtype)
     group = num_heads // num_kv_heads
-    if pooled is not None or value_dim != head_dim:
+    if (values_in_keys or sink is not None) and (logit_softcap or pooled is not None):
+      raise KernelError("latent rows and sinks go with neither a score cap nor pooled blocks")
+    if pooled is not None or value_dim != head_dim or values_in_keys or sink is not None:
       pool, pool_table, pool_len = pooled if pooled is not None else (None, None, 0)
       if pool is not None and pool.dtype != storage.dtype:
         raise KernelError("block entries and the cache must share one dtype")
@@ -833,7 +871,7 @@ class CudaOps:
         self._call("sb_paged_attention_general", _ptr(q), _code(q), _ptr(storage), _ptr(block_table),
                    block_table.shape[1], _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(out), t, num_heads,
                    num_kv_heads, head_dim, value_dim, ctx.page_size, storage.shape[0], float(logit_softcap),
-                   int(window or 0), *pool_args, _ptr(self.err))
+                   int(window or 0), *pool_args, int(values_in_keys), _ptr(sink), _ptr(self.err))
 
       # bfloat16 with key size = value size: the tensor-core tile kernel (mma.sync tiles of 64 rows,
       # the block entries in tiles of their own ahead of the tokens) for prompt portions and single
@@ -960,11 +998,145 @@ class CudaOps:
                _ptr(self.err))
     return q
 
-  def sigmoid_gate(self, x: torch.Tensor, proj: torch.Tensor, offset: int) -> torch.Tensor:
-    """x [T, N] *= sigmoid(proj[:, offset : offset + N]), in place."""
+  def sigmoid_gate(self, x: torch.Tensor, proj: torch.Tensor, offset: int, per: int = 1) -> torch.Tensor:
+    """x [T, N] *= sigmoid(proj[:, offset : offset + N / per]), one gate per `per` neighbours, in place."""
     gate = proj[:, offset:]
-    self._call("sb_sigmoid_gate", _ptr(x), gate.data_ptr(), proj.shape[1], _code(x), x.shape[0], x.shape[1])
+    self._call("sb_sigmoid_gate", _ptr(x), gate.data_ptr(), proj.shape[1], _code(x), x.shape[0], x.shape[1], int(per))
     return x
+
+  # ---- a residual stream kept several times -------------------------------------------------------
+  def spread_streams(self, h: torch.Tensor, copies: int) -> torch.Tensor:
+    lanes = self._new(h.shape[0], copies, h.shape[1], dtype=torch.float32)
+    self._call("sb_spread_streams", _ptr(h), _ptr(lanes), h.shape[0], copies, h.shape[1])
+    return lanes
+
+  def streams_step(self, lanes: torch.Tensor, branch: torch.Tensor | None, mix, out_w, weights, norm_weight,
+                   eps: float, plus_one: bool, rows: torch.Tensor | None) -> torch.Tensor | None:
+    """lanes [T, S, W] float32.  With `branch`: lanes[:, t] <- sum_s mix[s, t] lanes[:, s] + out_w[t] branch
+    (in place; with `rows` only those rows are computed and nothing is written).  With `weights`:
+    returns rms(sum_s weights[s] lanes[:, s]) * norm_weight in the activation dtype (`norm_weight`
+    None: the sum, float32).  One kernel (csrc/stream_mix.cu)."""
+    t, copies, width = lanes.shape
+    n = t if rows is None else rows.numel()
+    if branch is not None and branch.dtype != self.dtype:
+      branch = self.cast(branch, self.dtype)
+    y = y_sum = None
+    if weights is not None and norm_weight is not None:
+      y = self._new(n, width)
+    elif weights is not None:
+      y_sum = self._new(n, width, dtype=torch.float32)
+    self._call("sb_streams_step", _ptr(lanes), _ptr(branch), 0 if self.dtype == torch.float32 else 1, _ptr(mix),
+               _ptr(out_w), _ptr(weights), _ptr(norm_weight),
+               int(norm_weight is not None and norm_weight.dtype == torch.float32), float(eps), int(plus_one),
+               _ptr(rows), n, _ptr(y), _ptr(y_sum), copies, width, t, _ptr(self.err))
+    return y if y is not None else y_sum
+
+  def short_conv(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor | None,
+                 ctx: Any, *, activation: int = 0, residual: bool = False, offset: int = 0,
+                 channels: int | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Causal convolution over time per channel on x[:, offset : offset + channels] with the request's
+    last taps - 1 inputs in `state` [slots, taps - 1, channels] (csrc/stream_mix.cu)."""
+    channels = x.shape[1] - offset if channels is None else channels
+    taps = weight.shape[1]
+    out = self._new(x.shape[0], channels, dtype=out_dtype or self.dtype)
+    if out.dtype not in (x.dtype, torch.float32):
+      raise KernelError("a convolution's result is in its input's dtype or float32")
+    self._call("sb_short_conv", _ptr(x), x.shape[1], offset, _code(x), _ptr(weight), _ptr(bias), _ptr(state),
+               _ptr(ctx.token_seq), _ptr(ctx.cu_q), _ptr(ctx.slots), x.shape[0], ctx.num_seqs,
+               state.shape[0] if state is not None else 0, taps, channels, int(activation), int(residual),
+               int(out.dtype == torch.float32),
+               _ptr(out), _ptr(self.err))
+    self.launches += taps > 1
+    return out
+
+  def group_norm_gate(self, o: torch.Tensor, weight: torch.Tensor, eps: float, *, groups: int,
+                      gate: torch.Tensor | None = None, gate_offset: int = 0, gate_kind: str = "none") -> torch.Tensor:
+    """o float32 [T, N...], RMS-normed in `groups` equal parts, times weight [N]; the gate
+    gate[:, gate_offset : gate_offset + N] acts as silu before the norm or as sigmoid after it."""
+    t = o.shape[0]
+    n = o.numel() // max(t, 1)
+    kind = {"none": 0, "sigmoid_after": 1, "silu_before": 2}[gate_kind]
+    if kind and gate.dtype != self.dtype:
+      raise KernelError("the gate comes in the activation dtype")
+    out = self._new(t, n)
+    self._call("sb_group_norm_gate", _ptr(o), _ptr(gate) if kind else None, gate.shape[1] if kind else 0,
+               gate_offset, kind, _code(out), _ptr(weight), float(eps), t, n, groups, _ptr(out))
+    return out
+
+  def tanh_columns(self, x: torch.Tensor, offset: int, n: int) -> torch.Tensor:
+    out = self._new(x.shape[0], n, dtype=x.dtype)
+    self._call("sb_tanh_columns", _ptr(x), x.shape[1], offset, n, _code(x), _ptr(out), x.shape[0])
+    return out
+
+  def head_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [T, H * Din] . w [H, Dout, Din]^T per head -> [T, H * Dout] (csrc/stream_mix.cu)."""
+    h, dout, din = w.shape
+    if w.dtype != x.dtype:
+      raise KernelError("a product per head takes weights in the activations' dtype")
+    out = self._new(x.shape[0], h * dout, dtype=x.dtype)
+    self._call("sb_head_linear", _ptr(x), h * din, din, 0, _ptr(w), _code(x), h, din, dout, _ptr(out), h * dout, dout,
+               1.0, x.shape[0])
+    return out
+
+  # ---- attention over latents ---------------------------------------------------------------------
+  def latent_prepare(self, down: torch.Tensor, query_norm: torch.Tensor, kv_norm: torch.Tensor, eps: float,
+                     freq: torch.Tensor | None, *, query_rank: int, kv_rank: int, rotated_dim: int,
+                     storage: torch.Tensor | None, block_table: torch.Tensor, ctx: Any) -> torch.Tensor:
+    """Norms of both latents, the shared key part turned, the token's row [c | k_r] into its page;
+    returns the queries' latent [T, query_rank] (csrc/latent_attention.cu)."""
+    t = down.shape[0]
+    cq = self._new(t, query_rank, dtype=down.dtype)
+    if storage is not None and storage.dtype != down.dtype:
+      raise KernelError("the cache of latents is kept in the activation dtype")
+    self._call("sb_latent_prepare", _ptr(down), down.shape[1], _code(down), _ptr(query_norm), _ptr(kv_norm),
+               float(eps), _ptr(freq), freq.numel() if freq is not None else 0, query_rank, kv_rank, rotated_dim,
+               _ptr(ctx.positions), _ptr(ctx.token_seq), _ptr(block_table), block_table.shape[1], ctx.page_size,
+               storage.shape[0] if storage is not None else 0, _ptr(storage), _ptr(cq), t, _ptr(self.err))
+    return cq
+
+  def latent_queries(self, q: torch.Tensor, key_up_t: torch.Tensor, freq: torch.Tensor | None, scale: float,
+                     ctx: Any, *, num_heads: int, head_dim: int, rotated_dim: int) -> torch.Tensor:
+    """Per head [W_uk^T q_plain | turn(q_rot)] * scale: q [T, H (head_dim + rotated_dim)], key_up_t
+    [H, kv_rank, head_dim] -> [T, H (kv_rank + rotated_dim)]."""
+    t = q.shape[0]
+    rank = key_up_t.shape[1]
+    row_in, row_out = head_dim + rotated_dim, rank + rotated_dim
+    out = self._new(t, num_heads * row_out, dtype=q.dtype)
+    self._call("sb_head_linear", _ptr(q), num_heads * row_in, row_in, 0, _ptr(key_up_t), _code(q), num_heads, head_dim,
+               rank, _ptr(out), num_heads * row_out, row_out, float(scale), t)
+    self._call("sb_turn_query_part", _ptr(q), row_in, head_dim, _ptr(out), row_out, rank, _code(q), _ptr(freq),
+               freq.numel() if freq is not None else 0, rotated_dim, float(scale), _ptr(ctx.positions), t, num_heads)
+    return out
+
+  # ---- recurrent mixers with a matrix per head ------------------------------------------------------
+  def general_delta_scan(self, pre: torch.Tensor, low: torch.Tensor, decay_bias: torch.Tensor,
+                         removal_bias: torch.Tensor, state: torch.Tensor, ctx: Any, *, num_heads: int,
+                         head_dim: int) -> torch.Tensor:
+    """pre [T, r | k | v | gate | a | ...], low [T, heads * head_dim] -> float32 o [T, heads, head_dim];
+    walks every sequence's tokens through its state [slots, heads, head_dim, head_dim] (csrc/state_scans.cu)."""
+    t = pre.shape[0]
+    out = self._new(t, num_heads, head_dim, dtype=torch.float32)
+    scratch = self._new(t, num_heads * (6 * head_dim + 2), dtype=torch.float32)
+    self._call("sb_general_delta_scan", _ptr(pre), pre.shape[1], _ptr(low), low.shape[1], _code(pre), _ptr(decay_bias),
+               _ptr(removal_bias), _ptr(state), _ptr(ctx.cu_q), _ptr(ctx.slots), t, ctx.num_seqs, state.shape[0],
+               num_heads, head_dim, ctx.max_q_len, _ptr(scratch), _ptr(out), _ptr(self.err))
+    self.launches += 1
+    return out
+
+  def state_space_scan(self, xbc: torch.Tensor, pre: torch.Tensor, step_offset: int, step_bias: torch.Tensor,
+                       neg_rate: torch.Tensor, skip: torch.Tensor, state: torch.Tensor, ctx: Any, *, num_heads: int,
+                       value_dim: int, state_dim: int, num_groups: int) -> torch.Tensor:
+    """xbc float32 [T, x | B | C] after convolution and silu, the steps' sizes from pre[:, step_offset:]
+    -> float32 y [T, heads, value_dim]; state [slots, heads, state_dim, value_dim] (csrc/state_scans.cu)."""
+    t = xbc.shape[0]
+    out = self._new(t, num_heads, value_dim, dtype=torch.float32)
+    scratch = self._new(t, num_heads * 2, dtype=torch.float32)
+    self._call("sb_state_space_scan", _ptr(xbc), xbc.shape[1], _ptr(pre), pre.shape[1], _code(pre), step_offset,
+               _ptr(step_bias), _ptr(neg_rate), _ptr(skip), _ptr(state), _ptr(ctx.cu_q), _ptr(ctx.slots), t,
+               ctx.num_seqs, state.shape[0], num_heads, num_groups, state_dim, value_dim, ctx.max_q_len,
+               _ptr(scratch), _ptr(out), _ptr(self.err))
+    self.launches += 1
+    return out
 
   # ---- forget-gate recurrence ---------------------------------------------------
   def forget_gate_scan(self, pre: torch.Tensor, bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor,
@@ -995,6 +1167,15 @@ class CudaOps:
     self._call("sb_moe_route", _ptr(x), _code(x), t, width, _ptr(router), _ptr(correction), _ptr(shared_gate_w),
                router.shape[0], top, float(scale), int(score), int(renormalize), _ptr(chosen), _ptr(weight), _ptr(gate))
     return chosen, weight, gate
+
+  def route_by_table(self, token_ids: torch.Tensor, table: torch.Tensor, num_experts: int):
+    """chosen[t, j] = table[id_t, j] (int32 [T, top]) and the weights 1 / top (float32 [T, top])."""
+    t, top = token_ids.numel(), table.shape[1]
+    chosen = self._new(t, top, dtype=torch.int32)
+    weight = self._new(t, top, dtype=torch.float32)
+    self._call("sb_table_route", _ptr(token_ids), _ptr(table), table.shape[0], top, num_experts, _ptr(chosen),
+               _ptr(weight), t, _ptr(self.err))
+    return chosen, weight
 
   def _experts_one_by_one(self, x, sorted_pair, tiles, top, gate_up, down, activation) -> torch.Tensor:
     """The experts' products of a long prompt portion: the rows, sorted by expert, are gathered once,
@@ -1046,9 +1227,10 @@ class CudaOps:
 
   def mix_experts(self, x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, gate_up: torch.Tensor | None,
                   down: torch.Tensor | None, num_experts: int, activation: int, shared: torch.Tensor | None,
-                  shared_gate: torch.Tensor | None) -> torch.Tensor:
+                  shared_gate: torch.Tensor | None, gated: bool = True) -> torch.Tensor:
     """sum_j weight[t, j] * expert(chosen[t, j])(x[t]) + shared_gate[t] * shared[t]; experts with an
-    index >= num_experts return their input.  gate_up [E, 2F, W], down [E, W, F]."""
+    index >= num_experts return their input.  gate_up [E, 2F, W], down [E, W, F]; `gated` False:
+    experts without a gate, W_down act(W_up x), with gate_up [E, F, W]."""
     t, width = x.shape
     top = chosen.shape[1]
     pairs = t * top
@@ -1065,16 +1247,16 @@ class CudaOps:
                  _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]))
       hidden = down.shape[2]
       # (whole 16-byte groups per row, so that an expert's slice of the rows starts on a boundary)
-      if (x.dtype == torch.bfloat16 and 0 < self.expert_rows_for_dense_products * num_experts <= pairs
+      if (gated and x.dtype == torch.bfloat16 and 0 < self.expert_rows_for_dense_products * num_experts <= pairs
           and width % 8 == 0 and hidden % 8 == 0 and not torch.cuda.is_current_stream_capturing()):
         y_pair = self._experts_one_by_one(x, sorted_pair, tiles, top, gate_up, down, activation)
       else:
         h = self._new(pairs, hidden, dtype=x.dtype)
-        self._call("sb_moe_product", _ptr(x), _ptr(sorted_pair), top, _ptr(gate_up), _code(x), 1, width, hidden,
+        self._call("sb_moe_product", _ptr(x), _ptr(sorted_pair), top, _ptr(gate_up), _code(x), int(gated), width, hidden,
                    _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, activation, _ptr(h))
         y_pair = self._new(pairs, width, dtype=x.dtype)
         self._call("sb_moe_product", _ptr(h), None, 1, _ptr(down), _code(x), 0, hidden, width,
-                   _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, 0, _ptr(y_pair))
+                   _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, -1, _ptr(y_pair))
     else:
       pos.fill_(-1)
     if shared is not None and shared.dtype != x.dtype:
