@@ -124,7 +124,7 @@ def needle_case(window, heads=3):
   """A one-layer model whose query of token 1 is answered by the key of token 2 alone."""
   cfg_dict = zc.config([zc.latent(heads=heads, dim=12, rot_dim=8, vdim=10, dims=4, scale=1.0, window=window)],
                        [None], width=32, vocab=50, streams=2, taps=0)
-  cfg, t = zc.weights(cfg_dict, seed=11)
+  cfg, t = zc.weights(cfg_dict, seed=11, matrix_std=0.25)
   zc.plant_needle(cfg_dict, t, 0, needle=2, asker=1)
   return cfg_dict, t
 

@@ -84,7 +84,7 @@ def as_numpy(t):
   return {k: (v.float().numpy().astype(np.float64) if v.is_floating_point() else v.numpy()) for k, v in t.items()}
 
 
-def weights(cfg_dict, seed=0, matrix_std=0.25, scale_std=0.2):
+def weights(cfg_dict, seed=0, matrix_std=0.1, scale_std=0.2):
   """bfloat16-representable random weights by tensor name (CPU; integer tables stay integers)."""
   cfg = config_from_dict(cfg_dict)
   specs = DecoderModel(cfg.model_spec()).tensor_specs()
