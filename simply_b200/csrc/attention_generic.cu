@@ -228,7 +228,8 @@ extern "C" int sb_paged_attention_general(const void* q, int dtype, const void* 
                                           const float* sink, int* err, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (tied && (pool != nullptr || v_dim > head_dim)) return -13;
-  if (head_dim <= 0 || head_dim > 32 * GEN_MAX_DPL || v_dim <= 0 || v_dim > 32 * GEN_MAX_DPL) return -7;
+  // (the values' sums live in registers, GEN_MAX_DPL per lane; a key row only passes through)
+  if (head_dim <= 0 || head_dim > 4096 || v_dim <= 0 || v_dim > 32 * GEN_MAX_DPL) return -7;
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads) return -8;
   const long long items = (long long)num_tokens * num_q_heads;
   if (items > 0x7fffffffLL) return -6;

@@ -1,8 +1,8 @@
 """Prefill and decode throughput of a design beside the engine's closest other model at equal size
-(Generax beside Gemma 2, Sapivik beside Generax), and the time of every kernel call of one step of
-each with its share of the measured peaks.
+(Generax beside Gemma 2, Sapivik beside Generax, Zesapel beside Sapivik), and the time of every kernel
+call of one step of each with its share of the measured peaks.
 
-Used by `bench.py --design generax|sapivik` (the default benchmark does not import this file).  Layer
+Used by `bench.py --design generax|sapivik|zesapel` (the default benchmark does not import this file).  Layer
 shapes resemble a real model's; weights are random.  Per size and design:
 
 * prefill: one 2,048-token prompt in one step, median of 5 after 3 warm-up steps, CUDA events;
@@ -75,6 +75,25 @@ def sapivik_dict(s: dict) -> dict:
           "loop": {"start": 0, "stop": stop, "times": times if s["layers"] > stop else 1}, "max_context": 8192}
 
 
+def zesapel_dict(s: dict) -> dict:
+  """Latent attention, the generalized delta rule and the state-space mixer in turn (one layer in
+  three is attention, as in the Sapivik arm), each with table experts: sixteen of the hidden size of
+  a quarter of the dense one, four per token.  The latent of keys and values has four heads' size,
+  the rotated part half a head's; the recurrent states have heads of 64 channels; two streams and a
+  convolution of three taps on what every mixer reads."""
+  att = {"heads": s["heads"], "dim": s["dim"], "rot_dim": s["dim"] // 2, "vdim": s["dim"], "q_rank": s["width"] // 2,
+         "kv_rank": 4 * s["dim"], "scale": (s["dim"] + s["dim"] // 2) ** -0.5, "mask": {"size": WINDOW},
+         "rot": {"dims": s["dim"] // 2, "base": 10000.0}}
+  delta = {"heads": s["width"] // 64, "dim": 64}
+  ssm = {"heads": 2 * s["width"] // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": TAPS}
+  experts = {"kind": "moe", "expert": {"ff": s["ff"] // 4}, "router": {"experts": 16, "top": 4}}
+  kinds = (("latent_attention", att), ("general_delta", delta), ("mamba2", ssm))
+  layers = [{"type": kinds[i % 3][0], "mixer": dict(kinds[i % 3][1]), "mlp": dict(experts)} for i in range(s["layers"])]
+  return {"architecture": "Zesapel", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+          "embedding": {"scale": 1.0}, "max_positions": 8192, "streams": 2, "canon": {"taps": 3}, "decay_rank": RANK,
+          "layers": layers}
+
+
 def gemma2_dict(s: dict) -> dict:
   return {"architectures": ["Gemma2ForCausalLM"], "hidden_size": s["width"], "num_hidden_layers": s["layers"],
           "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": s["dim"],
@@ -129,7 +148,7 @@ class TimedOps:
         if args[3] is not None:
           flops = 2.0 * t_ * top_ * (args[3].shape[1] + args[4].shape[1]) * args[3].shape[2]
       if name in ("paged_attention", "project_rotate_store", "rope_and_cache_write", "qk_norm_rotate_store", "pool_blocks",
-                  "delta_rule_inputs", "gated_delta_scan", "rotate_headnorm_store", "forget_gate_scan"):
+                  "delta_rule_inputs", "gated_delta_scan", "rotate_headnorm_store", "forget_gate_scan", "latent_prepare"):
         moved -= big if name != "delta_rule_inputs" else 0  # the cache (or state) storage is not read whole
       if name == "paged_attention" and ctx is not None:
         q = args[0]
@@ -146,7 +165,7 @@ class TimedOps:
           pairs += int(keys.sum())
           seen += int(min(s0 + n, window + n)) + (int((s0 + n) // kw["pooled"][2]) if kw.get("pooled") is not None else 0)
         flops = 2.0 * pairs * heads * (dim + vdim)
-        moved += seen * kv_heads * (dim + vdim) * args[1].element_size()
+        moved += seen * kv_heads * (dim + (0 if kw.get("values_in_keys") else vdim)) * args[1].element_size()
       if name == "gated_delta_scan" and ctx is not None:
         state = args[5]
         per_slot = state[0].numel() * 4
@@ -155,6 +174,12 @@ class TimedOps:
       if name == "forget_gate_scan" and ctx is not None:
         moved += 2 * args[3][0].numel() * 4 * ctx.num_seqs
         flops = 5.0 * args[0].shape[0] * kw["num_heads"] * kw["head_dim"] * kw["value_dim"]
+      if name in ("general_delta_scan", "state_space_scan") and ctx is not None:
+        state = args[4] if name == "general_delta_scan" else args[6]
+        moved += 2 * state[0].numel() * 4 * ctx.num_seqs - _nbytes(state)
+        per_token = (8.0 * kw["num_heads"] * kw["head_dim"] ** 2 if name == "general_delta_scan" else
+                     5.0 * kw["num_heads"] * kw["state_dim"] * kw["value_dim"])
+        flops = per_token * out.shape[0]
       self.rows.append((name, out.shape[0] if isinstance(out, torch.Tensor) else 0, e0.elapsed_time(e1), moved, flops))
       return out
 
@@ -209,8 +234,8 @@ def _prefill_ms(engine, tokens: int, vocab: int) -> float:
   return float(np.median(times))
 
 
-PAIRS = {"generax": ("generax", "gemma2"), "sapivik": ("sapivik", "generax")}
-DICTS = {"generax": generax_dict, "gemma2": gemma2_dict, "sapivik": sapivik_dict}
+PAIRS = {"generax": ("generax", "gemma2"), "sapivik": ("sapivik", "generax"), "zesapel": ("zesapel", "sapivik")}
+DICTS = {"generax": generax_dict, "gemma2": gemma2_dict, "sapivik": sapivik_dict, "zesapel": zesapel_dict}
 
 
 def run(args, peaks: dict, time_decode, design: str = "generax") -> dict:

@@ -39,9 +39,13 @@ class KernelBuildError(RuntimeError):
 PER_HEAD_DIM = ("attention_mma.cu", "attention_tc.cu", "attention_tc_pair.cu")
 
 
+# Compiled once per shape of a cache of latents (-DSB_LATENT_KD=N -DSB_LATENT_VD=M).
+PER_LATENT_SHAPE = ("attention_latent_mma.cu",)
+
+
 def sources() -> list[str]:
   return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC)
-                if f.endswith(".cu") and f not in PER_HEAD_DIM)
+                if f.endswith(".cu") and f not in PER_HEAD_DIM + PER_LATENT_SHAPE)
 
 
 def _headers() -> list[str]:
@@ -100,6 +104,27 @@ def build_attention(head_dim: int, verbose: bool = True, force: bool = False) ->
     raise KernelBuildError(f"tensor-core attention takes head sizes 16, 32, ..., 256; got {head_dim}")
   srcs = [os.path.join(CSRC, f) for f in PER_HEAD_DIM]
   return _build(srcs, attention_lib_name(head_dim), [f"-DSB_HEAD_DIM={head_dim}"], verbose, force)
+
+
+def latent_shape_ok(row_dim: int, value_dim: int) -> bool:
+  """Shapes the tensor-core kernel over latents takes: rows of a multiple of 16 numbers up to 768
+  whose first `value_dim` (a multiple of 16 up to 256, or of 32 up to 512) are the value."""
+  groups = (value_dim + 255) // 256
+  return (row_dim % 16 == 0 and 16 <= row_dim <= 768 and 16 <= value_dim <= min(row_dim, 512)
+          and value_dim % (16 * groups) == 0)
+
+
+def latent_lib_name(row_dim: int, value_dim: int) -> str:
+  return f"libsimply_b200_latent_k{row_dim}_v{value_dim}.so"
+
+
+def build_latent_attention(row_dim: int, value_dim: int, verbose: bool = True, force: bool = False) -> str:
+  """Compiles the tensor-core attention over latents for one shape; returns the library's path."""
+  if not latent_shape_ok(row_dim, value_dim):
+    raise KernelBuildError(f"tensor-core attention over latents does not take rows of {row_dim} with values of {value_dim}")
+  srcs = [os.path.join(CSRC, f) for f in PER_LATENT_SHAPE]
+  return _build(srcs, latent_lib_name(row_dim, value_dim),
+                [f"-DSB_LATENT_KD={row_dim}", f"-DSB_LATENT_VD={value_dim}"], verbose, force)
 
 
 def _build(srcs: list[str], lib_name: str, defines: list[str], verbose: bool, force: bool) -> str:
@@ -174,4 +199,17 @@ def load_attention(head_dim: int) -> ctypes.CDLL:
     if lib is None:
       lib = ctypes.CDLL(build_attention(head_dim))
       _attention_libs[head_dim] = lib
+    return lib
+
+
+_latent_libs: dict[tuple[int, int], ctypes.CDLL] = {}
+
+
+def load_latent_attention(row_dim: int, value_dim: int) -> ctypes.CDLL:
+  """Builds if needed and loads the library for one shape of a cache of latents."""
+  with _lock:
+    lib = _latent_libs.get((row_dim, value_dim))
+    if lib is None:
+      lib = ctypes.CDLL(build_latent_attention(row_dim, value_dim))
+      _latent_libs[(row_dim, value_dim)] = lib
     return lib

@@ -154,6 +154,7 @@ class CudaOps:
     self._declare()
     self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
     self._attn_fns: dict[int, tuple] = {}
+    self._latent_fns: dict[tuple[int, int], Any] = {}
     self._tensor_maps: dict[tuple, tuple] = {}
     # Work counter of the split-key attention kernel: zero between launches (its merge kernel resets it).
     self._attn_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -420,6 +421,18 @@ class CudaOps:
       self._decode_slots[head_dim] = slots
       fns = self._attn_fns[head_dim] = (prefill, decode, make_map, prefill_tc, prefill_pair, prefill_pooled)
     return fns
+
+  def _latent_fn(self, row_dim: int, value_dim: int):
+    fn = self._latent_fns.get((row_dim, value_dim))
+    if fn is None:
+      lib = build.load_latent_attention(row_dim, value_dim)
+      c_int, c_void = ctypes.c_int, ctypes.c_void_p
+      fn = getattr(lib, f"sb_latent_attention_k{row_dim}_v{value_dim}")
+      fn.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
+                     c_int, c_int, c_void, c_void]
+      fn.restype = c_int
+      self._latent_fns[(row_dim, value_dim)] = fn
+    return fn
 
   def decode_chunk_for(self, kv_lo: Sequence[int], kv_hi: Sequence[int], num_kv_heads: int, head_dim: int) -> int:
     """Chunk length of split-key attention for sequences that see the keys [kv_lo, kv_hi).
@@ -876,6 +889,17 @@ class CudaOps:
       # bfloat16 with key size = value size: the tensor-core tile kernel (mma.sync tiles of 64 rows,
       # the block entries in tiles of their own ahead of the tokens) for prompt portions and single
       # tokens alike; other shapes and float32: the general kernel.
+      if (values_in_keys and pooled is None and num_kv_heads == 1 and q.dtype == torch.bfloat16
+          and self.tensor_core_attention and build.latent_shape_ok(head_dim, value_dim)):
+        # a cache of latents in bfloat16: the tensor-core kernel of this shape (csrc/attention_latent_mma.cu)
+        rc = self._latent_fn(head_dim, value_dim)(
+            _ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_q), _ptr(ctx.q_start),
+            _ptr(out), _ptr(sink), t, ctx.num_seqs, ctx.max_q_len, num_heads, ctx.page_size, storage.shape[0],
+            int(window or 0), _ptr(self.err), self._stream())
+        self.launches += 1
+        if rc:
+          raise KernelError(f"sb_latent_attention: {_STATUS.get(rc, rc)}")
+        return out
       tensor_cores = (pooled is not None and value_dim == head_dim and q.dtype == torch.bfloat16 and window
                       and self._uses_tensor_core_attention(head_dim, group))
       if not tensor_cores:

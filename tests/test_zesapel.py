@@ -108,7 +108,8 @@ def test_larger_sizes_and_pages_of_64(dtype):
       [zc.moe(experts=8, top=2, ff=64), zc.moe(experts=3, top=1, ff=128), None, zc.moe(experts=5, top=3, ff=32),
        zc.moe(experts=4, top=2, ff=64)],
       width=128, vocab=300, streams=2, taps=3, rank=16)
-  cfg, t = zc.weights(cfg_dict, seed=3, matrix_std=0.1)
+  # (matrices of this size at std 0.1 put the bfloat16 rounding noise of 99,000 logits at the bound itself)
+  cfg, t = zc.weights(cfg_dict, seed=3, matrix_std=0.06)
   engine = zc.build_engine(cfg, t, dtype, "cuda", None, page_size=64, slots=2, max_seq_len=512)
   toks = tokens_for(cfg_dict, 330, 1)
   want = plain.forward(cfg_dict, zc.as_numpy(t), toks)
@@ -118,21 +119,45 @@ def test_larger_sizes_and_pages_of_64(dtype):
   engine.ops.check_errors()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [(1, 32, 16, 70), (2, 16, 16, 33), (20, 64, 16, 100), (24, 288, 32, 150),
+                                   (5, 512, 64, None), (3, 96, 160, 64)])
+def test_latent_rows_of_every_tile_shape(shape, dtype):
+  """Attention over latents alone at shapes that take each form of its tensor-core kernel in
+  bfloat16 (single tokens of up to 16, up to 32 and more rows; tiles of 32 and of 64 keys; one and
+  two groups of value columns; heads that do not divide a tile), over several pages and tiles."""
+  heads, kv_rank, rot_dim, window = shape
+  cfg_dict = zc.config([zc.latent(heads=heads, dim=8, rot_dim=rot_dim, vdim=8, q_rank=24, kv_rank=kv_rank, dims=rot_dim // 2,
+                                  scale=0.1, window=window)], [None], width=64, vocab=70, streams=0, taps=0)
+  cfg, t = zc.weights(cfg_dict, seed=4)
+  engine = zc.build_engine(cfg, t, dtype, "cuda", None, page_size=64, slots=2, max_seq_len=512)
+  toks = tokens_for(cfg_dict, 300, 2)
+  want = plain.forward(cfg_dict, zc.as_numpy(t), toks)
+  for what, cuts in [("whole", [300]), ("portions", zc.cuts_of(300, [97, 2, 31, 64, 3, 1, 70])),
+                     ("decoding", [230] + [1] * 70)]:
+    zc.check_close(zc.run_cuts(engine, toks, cuts), want, dtype, f"{shape}: {what}")
+  engine.ops.check_errors()
+
+
 # ---- a key that stands out ----------------------------------------------------------------------
 
-def needle_case(window, heads=3):
-  """A one-layer model whose query of token 1 is answered by the key of token 2 alone."""
-  cfg_dict = zc.config([zc.latent(heads=heads, dim=12, rot_dim=8, vdim=10, dims=4, scale=1.0, window=window)],
+def needle_case(window, heads=3, tiles=False):
+  """A one-layer model whose query of token 1 is answered by the key of token 2 alone.  `tiles`: cached
+  rows of a size that the tensor-core kernel over latents takes."""
+  sizes = dict(rot_dim=16, kv_rank=32) if tiles else dict(rot_dim=8)
+  cfg_dict = zc.config([zc.latent(heads=heads, dim=12, vdim=10, dims=4, scale=1.0, window=window, **sizes)],
                        [None], width=32, vocab=50, streams=2, taps=0)
-  cfg, t = zc.weights(cfg_dict, seed=11, matrix_std=0.25)
+  cfg, t = zc.weights(cfg_dict, seed=11, matrix_std=0.12 if tiles else 0.25)  # (equal rounding noise at both sizes)
   zc.plant_needle(cfg_dict, t, 0, needle=2, asker=1)
   return cfg_dict, t
 
 
 @pytest.mark.parametrize("where", WHERE)
-def test_a_key_that_stands_out_at_every_edge_of_the_window(where):
+@pytest.mark.parametrize("tiles", [False, True])
+def test_a_key_that_stands_out_at_every_edge_of_the_window(tiles, where):
   window = 12
-  cfg_dict, t = needle_case(window)
+  cfg_dict, t = needle_case(window, tiles=tiles)
   w = zc.as_numpy(t)
   rng = np.random.default_rng(0)
   engine, _ = engine_for(cfg_dict, where, tensors=t, page_size=4)
@@ -156,8 +181,9 @@ def test_a_key_that_stands_out_at_every_edge_of_the_window(where):
 
 
 @pytest.mark.parametrize("where", WHERE)
-def test_a_far_key_among_hundreds_without_a_window(where):
-  cfg_dict, t = needle_case(None, heads=2)
+@pytest.mark.parametrize("tiles", [False, True])
+def test_a_far_key_among_hundreds_without_a_window(tiles, where):
+  cfg_dict, t = needle_case(None, heads=2, tiles=tiles)
   w = zc.as_numpy(t)
   rng = np.random.default_rng(1)
   engine, _ = engine_for(cfg_dict, where, tensors=t, page_size=16, max_seq_len=512, slots=2)
