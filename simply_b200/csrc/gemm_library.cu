@@ -22,6 +22,7 @@ struct LtApi {
   decltype(&cublasLtMatmulDescSetAttribute) desc_set;
   decltype(&cublasLtMatrixLayoutCreate) layout_create;
   decltype(&cublasLtMatrixLayoutDestroy) layout_destroy;
+  decltype(&cublasLtMatrixLayoutSetAttribute) layout_set;
   decltype(&cublasLtMatmulPreferenceCreate) pref_create;
   decltype(&cublasLtMatmulPreferenceSetAttribute) pref_set;
   decltype(&cublasLtMatmulPreferenceDestroy) pref_destroy;
@@ -50,6 +51,7 @@ LtApi* lt_api() {
   SB_SYM(desc_set, cublasLtMatmulDescSetAttribute)
   SB_SYM(layout_create, cublasLtMatrixLayoutCreate)
   SB_SYM(layout_destroy, cublasLtMatrixLayoutDestroy)
+  SB_SYM(layout_set, cublasLtMatrixLayoutSetAttribute)
   SB_SYM(pref_create, cublasLtMatmulPreferenceCreate)
   SB_SYM(pref_set, cublasLtMatmulPreferenceSetAttribute)
   SB_SYM(pref_destroy, cublasLtMatmulPreferenceDestroy)
@@ -153,6 +155,61 @@ extern "C" int sb_gemm_library_bf16(const void* x, const void* w, void* out, int
                          workspace, c.workspace, stream);
     }
     rc = st == CUBLAS_STATUS_SUCCESS ? 0 : (st == CUBLAS_STATUS_NOT_SUPPORTED ? -9 : (int)st);
+  }
+  drop_layouts(api, l);
+  return rc;
+}
+
+// One product per head in one call: out[:, h] = alpha * x[:, h] . w[h]^T with x [M, x_stride] whose head h
+// starts at column h * x_head, w [H, N, K], out [M, out_stride] whose head h starts at h * out_head.
+// Returns as sb_gemm_library_bf16 does.
+extern "C" int sb_gemm_library_bf16_heads(const void* x, int x_stride, int x_head, const void* w, void* out,
+                                          int out_stride, int out_head, int M, int H, int N, int K, float alpha,
+                                          void* workspace, long long workspace_bytes, cudaStream_t stream) {
+  if (M == 0 || N == 0 || H == 0) return 0;
+  if (K <= 0 || K % 8 || N % 8 || x_stride % 8 || x_head % 8 || out_stride % 8 || out_head % 8) return -9;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  LtApi* api = lt_api();
+  if (!api) return -9;
+  Layouts l;
+  int rc = -9;
+  const int32_t batch = H;
+  const int64_t sa = (int64_t)N * K, sb = x_head, sc = out_head;
+  auto batched = [&](cublasLtMatrixLayout_t m, int64_t stride) {
+    return api->layout_set(m, CUBLASLT_MATRIX_LAYOUT_BATCH_COUNT, &batch, sizeof(batch)) == CUBLAS_STATUS_SUCCESS &&
+           api->layout_set(m, CUBLASLT_MATRIX_LAYOUT_STRIDED_BATCH_OFFSET, &stride, sizeof(stride)) == CUBLAS_STATUS_SUCCESS;
+  };
+  if (api->layout_create(&l.a, CUDA_R_16BF, K, N, K) == CUBLAS_STATUS_SUCCESS &&
+      api->layout_create(&l.b, CUDA_R_16BF, K, M, x_stride) == CUBLAS_STATUS_SUCCESS &&
+      api->layout_create(&l.c, CUDA_R_16BF, N, M, out_stride) == CUBLAS_STATUS_SUCCESS && batched(l.a, sa) &&
+      batched(l.b, sb) && batched(l.c, sc)) {
+    // (the algorithm is looked up per call: a handful of calls per step, each worth a GFLOP or more)
+    static std::map<std::tuple<int, int, int, int, int, int, int, int, long long>, Chosen> chosen;
+    const auto key = std::make_tuple(M, H, N, K, x_stride, x_head, out_stride, out_head, workspace_bytes);
+    auto it = chosen.find(key);
+    bool found = it != chosen.end();
+    if (!found) {
+      cublasLtMatmulPreference_t pref = nullptr;
+      if (api->pref_create(&pref) == CUBLAS_STATUS_SUCCESS) {
+        const size_t bytes = (size_t)workspace_bytes;
+        api->pref_set(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &bytes, sizeof(bytes));
+        cublasLtMatmulHeuristicResult_t result;
+        int count = 0;
+        if (api->heuristic(api->handle, api->op, l.a, l.b, l.c, l.c, pref, 1, &result, &count) == CUBLAS_STATUS_SUCCESS &&
+            count > 0) {
+          if (chosen.size() > 256) chosen.clear();
+          it = chosen.emplace(key, Chosen{result.algo, result.workspaceSize}).first;
+          found = true;
+        }
+        api->pref_destroy(pref);
+      }
+    }
+    if (found) {
+      const float beta = 0.0f;
+      cublasStatus_t st = api->matmul(api->handle, api->op, &alpha, w, l.a, x, l.b, &beta, out, l.c, out, l.c,
+                                      &it->second.algo, workspace, it->second.workspace, stream);
+      rc = st == CUBLAS_STATUS_SUCCESS ? 0 : (st == CUBLAS_STATUS_NOT_SUPPORTED ? -9 : (int)st);
+    }
   }
   drop_layouts(api, l);
   return rc;

@@ -520,10 +520,29 @@ extern "C" int sb_gemm_gated_tc(const void* x, const void* w, void* out, int M, 
 extern "C" int sb_gemm_library_bf16(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,
                                     void* workspace, long long workspace_bytes, cudaStream_t stream);
 
+// h <- act(h) in place, eight numbers per thread (experts without a gate on the dense route).
+__global__ void __launch_bounds__(256) activate_rows_kernel(bf16* __restrict__ h, long long groups, int act) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= groups) return;
+  uint4 v = reinterpret_cast<uint4*>(h)[i];
+  __nv_bfloat162* pair = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(pair[e]);
+    pair[e] = __floats2bfloat162_rn(moe_activation(f.x, act), moe_activation(f.y, act));
+  }
+  reinterpret_cast<uint4*>(h)[i] = v;
+}
+
+// `gated` 0: experts without a gate, gate_up [E, hidden, width]: the library's product, the
+// activation in place, the library's product.
 extern "C" int sb_experts_dense_bf16(const void* xs, const void* gate_up, const void* down, void* h, void* y,
                                      const int* starts, const int* counts, const int* experts, int num, int width,
-                                     int hidden, int act, int blocks, int pairs, void* workspace, void* workspace2,
-                                     long long workspace_bytes, int* done, int* err, cudaStream_t stream) {
+                                     int hidden, int act, int gated, int blocks, int pairs, void* workspace,
+                                     void* workspace2, long long workspace_bytes, int* done, int* err,
+                                     cudaStream_t stream) {
   *done = 0;
   static cudaStream_t side = nullptr;
   static cudaEvent_t fork_event = nullptr, join_event = nullptr;
@@ -553,10 +572,19 @@ extern "C" int sb_experts_dense_bf16(const void* xs, const void* gate_up, const 
     const size_t row = (size_t)starts[i];
     const bf16* x_i = (const bf16*)xs + row * width;
     bf16* h_i = (bf16*)h + row * hidden;
-    const bf16* gu = (const bf16*)gate_up + (size_t)experts[i] * 2 * hidden * width;
+    const bf16* gu = (const bf16*)gate_up + (size_t)experts[i] * (gated ? 2 : 1) * hidden * width;
     const bf16* dn = (const bf16*)down + (size_t)experts[i] * width * hidden;
-    int rc = sb_gemm_gated_tc(x_i, gu, h_i, counts[i], hidden, width, act, 0.f, blocks, pairs, err, stream);
-    if (rc != 0) return rc;
+    int rc;
+    if (gated) {
+      rc = sb_gemm_gated_tc(x_i, gu, h_i, counts[i], hidden, width, act, 0.f, blocks, pairs, err, stream);
+      if (rc != 0) return rc;
+    } else {
+      rc = sb_gemm_library_bf16(x_i, gu, h_i, counts[i], hidden, width, 0, workspace, workspace_bytes, stream);
+      if (rc != 0) return rc;
+      const long long groups = (long long)counts[i] * hidden / 8;  // (hidden is a multiple of 8, rows start on 16 bytes)
+      sb_launch(activate_rows_kernel, dim3((unsigned)((groups + 255) / 256)), 256, 0, stream, h_i, groups, act);
+      SB_LAUNCH_CHECK();
+    }
     rc = sb_gemm_library_bf16(h_i, dn, (bf16*)y + row * width, counts[i], width, hidden, 0, workspace, workspace_bytes,
                               stream);
     if (rc != 0) return rc;  // (h_i is computed; the caller redoes this expert whole)

@@ -148,23 +148,46 @@ general_delta_scan_kernel(const float* __restrict__ vecs, const float* __restric
     }
     __syncthreads();
     const float* buf = stage + (size_t)which * chunk * per_token;
-    for (int i = 0; i < count; ++i) {
+    // A token's vectors are fetched into registers while the token before it is worked on: the walk
+    // is a chain of dependent steps per token, and the fetches' latency would otherwise be part of it.
+    float cw[ROWS], cu[ROWS], ca[ROWS], ck[ROWS], cr[ROWS], cv, cra, crk;
+    auto fetch = [&](int i, float (&fw)[ROWS], float (&fu)[ROWS], float (&fa)[ROWS], float (&fk)[ROWS],
+                     float (&fr)[ROWS], float& fv, float& fra, float& frk) {
       const float* w = buf + (size_t)i * per_token;
-      const float* u = w + d;
-      const float* au = w + 2 * d;
-      const float* k = w + 3 * d;
-      const float* rr = w + 4 * d;
-      const float vj = w[5 * d + min(col_local, cols - 1)];
-      const float ra = w[5 * d + cols_pad], rk = w[5 * d + cols_pad + 1];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const int row = min(rs + RS * r, d - 1);
+        fw[r] = w[row];
+        fu[r] = w[d + row];
+        fa[r] = w[2 * d + row];
+        fk[r] = w[3 * d + row];
+        fr[r] = w[4 * d + row];
+      }
+      fv = w[5 * d + min(col_local, cols - 1)];
+      fra = w[5 * d + cols_pad];
+      frk = w[5 * d + cols_pad + 1];
+    };
+    constexpr bool AHEAD = ROWS <= 8;  // (two tokens' vectors of 32 rows do not fit the registers)
+    if constexpr (AHEAD) fetch(0, cw, cu, ca, ck, cr, cv, cra, crk);
+    for (int i = 0; i < count; ++i) {
+      float nw[ROWS], nu[ROWS], na[ROWS], nk[ROWS], nr[ROWS], nv, nra, nrk;
+      const float* here = buf + (size_t)i * per_token;  // (32 rows per lane: read where they are used)
+      if constexpr (AHEAD) {
+        fetch(min(i + 1, count - 1), nw, nu, na, nk, nr, nv, nra, nrk);
+      } else {
+        cv = here[5 * d + min(col_local, cols - 1)];
+        cra = here[5 * d + cols_pad];
+        crk = here[5 * d + cols_pad + 1];
+      }
       // One pass over the old state gives both sums: o = r . (w * s) - p (r . a u) + v_j (r . k).
       float p = 0.f, od = 0.f;
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) {
         const int row = rs + RS * r;
         if (row < d) {
-          p = fmaf(u[row], s[r], p);
-          s[r] *= w[row];
-          od = fmaf(rr[row], s[r], od);
+          p = fmaf(AHEAD ? cu[r] : here[d + row], s[r], p);
+          s[r] *= AHEAD ? cw[r] : here[row];
+          od = fmaf(AHEAD ? cr[r] : here[4 * d + row], s[r], od);
         }
       }
 #pragma unroll
@@ -175,9 +198,16 @@ general_delta_scan_kernel(const float* __restrict__ vecs, const float* __restric
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) {
         const int row = rs + RS * r;
-        if (row < d) s[r] = fmaf(k[row], vj, fmaf(-au[row], p, s[r]));
+        if (row < d) s[r] = fmaf(AHEAD ? ck[r] : here[3 * d + row], cv, fmaf(-(AHEAD ? ca[r] : here[2 * d + row]), p, s[r]));
       }
-      if (on && rs == 0) out[((size_t)(first + base + i) * H + h) * d + col] = fmaf(vj, rk, fmaf(-p, ra, od));
+      if (on && rs == 0) out[((size_t)(first + base + i) * H + h) * d + col] = fmaf(cv, crk, fmaf(-p, cra, od));
+      if constexpr (AHEAD) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          cw[r] = nw[r]; cu[r] = nu[r]; ca[r] = na[r]; ck[r] = nk[r]; cr[r] = nr[r];
+        }
+        cv = nv; cra = nra; crk = nrk;
+      }
     }
     __syncthreads();  // the buffer is filled again two chunks on
   }
@@ -338,6 +368,9 @@ state_space_scan_kernel(const float* __restrict__ xbc, int C, const float* __res
     }
     __syncthreads();
     const float* buf = stage + (size_t)which * chunk * per_token;
+    // (a token's update of the state does not wait for the sum that reads it: four tokens at a time let
+    // the fetches, updates and sums over lanes of neighbouring tokens overlap)
+#pragma unroll(ROWS <= 8 ? 4 : 1)
     for (int i = 0; i < count; ++i) {
       const float* bm = buf + (size_t)i * per_token;
       const float* cm = bm + n_pad;

@@ -312,9 +312,12 @@ class CudaOps:
       fn.restype = c_int
     self.lib.sb_gemm_library_bf16.argtypes = [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_void, c_ll, c_void]
     self.lib.sb_gemm_library_bf16.restype = c_int
+    self.lib.sb_gemm_library_bf16_heads.argtypes = [c_void, c_int, c_int, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
+                                                    c_int, ctypes.c_float, c_void, c_ll, c_void]
+    self.lib.sb_gemm_library_bf16_heads.restype = c_int
     c_ip = ctypes.POINTER(c_int)
     self.lib.sb_experts_dense_bf16.argtypes = [c_void, c_void, c_void, c_void, c_void, c_ip, c_ip, c_ip, c_int, c_int,
-                                               c_int, c_int, c_int, c_int, c_void, c_void, c_ll, c_ip, c_void, c_void]
+                                               c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_ll, c_ip, c_void, c_void]
     self.lib.sb_experts_dense_bf16.restype = c_int
     self.lib.sb_graph_burst.argtypes = [c_void, c_void, c_void, c_ll, c_int, c_void, c_void, c_ll, c_void]
     self.lib.sb_graph_burst.restype = c_int
@@ -345,6 +348,24 @@ class CudaOps:
                                        _ptr(workspace), workspace.numel(), stream)
     if rc > 0:
       raise KernelError(f"sb_gemm_library_bf16: cuBLAS status {rc}")
+    self.launches += rc == 0
+    return rc == 0
+
+  def _library_head_products(self, x: torch.Tensor, x_head: int, w: torch.Tensor, out: torch.Tensor, out_head: int,
+                             alpha: float) -> bool:
+    """out[:, h * out_head : + N] = alpha * x[:, h * x_head : + K] . w[h]^T for w [H, N, K], all heads in one
+    call of the matrix-product library (bfloat16, from 17 rows); False when it does not take the shape."""
+    if x.dtype != torch.bfloat16 or x.shape[0] <= self.skinny_max_rows or not self.direct_library_products:
+      return False
+    stream = self._stream()
+    workspace = self._library_workspaces.get(stream.value)
+    if workspace is None:
+      workspace = self._library_workspaces[stream.value] = torch.empty(32 << 20, dtype=torch.uint8, device=self.device)
+    h, n, k = w.shape
+    rc = self.lib.sb_gemm_library_bf16_heads(_ptr(x), x.shape[1], x_head, _ptr(w), _ptr(out), out.shape[1], out_head,
+                                             x.shape[0], h, n, k, float(alpha), _ptr(workspace), workspace.numel(), stream)
+    if rc > 0:
+      raise KernelError(f"sb_gemm_library_bf16_heads: cuBLAS status {rc}")
     self.launches += rc == 0
     return rc == 0
 
@@ -1098,8 +1119,9 @@ class CudaOps:
     if w.dtype != x.dtype:
       raise KernelError("a product per head takes weights in the activations' dtype")
     out = self._new(x.shape[0], h * dout, dtype=x.dtype)
-    self._call("sb_head_linear", _ptr(x), h * din, din, 0, _ptr(w), _code(x), h, din, dout, _ptr(out), h * dout, dout,
-               1.0, x.shape[0])
+    if not self._library_head_products(x, din, w, out, dout, 1.0):
+      self._call("sb_head_linear", _ptr(x), h * din, din, 0, _ptr(w), _code(x), h, din, dout, _ptr(out), h * dout, dout,
+                 1.0, x.shape[0])
     return out
 
   # ---- attention over latents ---------------------------------------------------------------------
@@ -1126,8 +1148,9 @@ class CudaOps:
     rank = key_up_t.shape[1]
     row_in, row_out = head_dim + rotated_dim, rank + rotated_dim
     out = self._new(t, num_heads * row_out, dtype=q.dtype)
-    self._call("sb_head_linear", _ptr(q), num_heads * row_in, row_in, 0, _ptr(key_up_t), _code(q), num_heads, head_dim,
-               rank, _ptr(out), num_heads * row_out, row_out, float(scale), t)
+    if not self._library_head_products(q, row_in, key_up_t, out, row_out, scale):
+      self._call("sb_head_linear", _ptr(q), num_heads * row_in, row_in, 0, _ptr(key_up_t), _code(q), num_heads, head_dim,
+                 rank, _ptr(out), num_heads * row_out, row_out, float(scale), t)
     self._call("sb_turn_query_part", _ptr(q), row_in, head_dim, _ptr(out), row_out, rank, _code(q), _ptr(freq),
                freq.numel() if freq is not None else 0, rotated_dim, float(scale), _ptr(ctx.positions), t, num_heads)
     return out
@@ -1201,13 +1224,14 @@ class CudaOps:
                _ptr(weight), t, _ptr(self.err))
     return chosen, weight
 
-  def _experts_one_by_one(self, x, sorted_pair, tiles, top, gate_up, down, activation) -> torch.Tensor:
+  def _experts_one_by_one(self, x, sorted_pair, tiles, top, gate_up, down, activation, gated=True) -> torch.Tensor:
     """The experts' products of a long prompt portion: the rows, sorted by expert, are gathered once,
     the host reads how many each expert got (the one wait of the step), and every expert's rows go
     through the engine's own products for a dense feed-forward (the tcgen05 kernel with the
     activation on its sums from 129 rows, the library's product for the way down), issued by one
-    native call that puts every other expert on a second stream (csrc/moe.cu).  Returns the rows of
-    every pair in sorted order, as the grouped kernel does."""
+    native call that puts every other expert on a second stream (csrc/moe.cu).  Experts without a
+    gate: the library's product both ways, the activation in place between them.  Returns the rows
+    of every pair in sorted order, as the grouped kernel does."""
     expert, row0, count = tiles.cpu().numpy()
     total = int(count[expert >= 0].sum())  # (identity experts' pairs have no row; the list's tail is unused)
     rows_of = torch.div(sorted_pair[:total], top, rounding_mode="floor")
@@ -1219,7 +1243,10 @@ class CudaOps:
     y = self._new(total, width, dtype=x.dtype)
     # Experts with enough rows for the tcgen05 product: all of them in one call of the library, so
     # that the host pays one call, not two per expert.  The others through the kernel table's methods.
-    big = counts >= self.gated_tc_min_rows if self.gated_tc_min_rows > 0 else np.zeros(len(counts), dtype=bool)
+    if not gated:
+      big = np.ones(len(counts), dtype=bool)
+    else:
+      big = counts >= self.gated_tc_min_rows if self.gated_tc_min_rows > 0 else np.zeros(len(counts), dtype=bool)
     rest = [(int(e), int(s), int(n)) for e, s, n in zip(which[~big], starts[~big], counts[~big])]
     which, starts, counts = (np.ascontiguousarray(a[big]) for a in (which, starts, counts))
     if len(which):
@@ -1237,12 +1264,14 @@ class CudaOps:
       as_ints = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))
       rc = self.lib.sb_experts_dense_bf16(
           _ptr(xs), _ptr(gate_up), _ptr(down), _ptr(h), _ptr(y), as_ints(starts), as_ints(counts), as_ints(which),
-          len(which), width, hidden, activation, self.gated_tc_blocks, int(self.gated_tc_pairs), _ptr(workspace),
+          len(which), width, hidden, activation, int(gated), self.gated_tc_blocks, int(self.gated_tc_pairs), _ptr(workspace),
           _ptr(second), workspace.numel(), ctypes.byref(finished), _ptr(self.err), stream)
       if rc > 0:
         raise KernelError(f"sb_experts_dense_bf16: CUDA or cuBLAS status {rc}")
       done = finished.value
-      self.launches += 2 * done
+      if not gated and done < len(which):
+        raise KernelError("sb_experts_dense_bf16: the library refused a product")
+      self.launches += (2 if gated else 3) * done
       rest += list(zip(which[done:].tolist(), starts[done:].tolist(), counts[done:].tolist()))
     for e, start, n in rest:
       h_e = self.gated_linear(xs[start:start + n], gate_up[e], activation)
@@ -1271,9 +1300,9 @@ class CudaOps:
                  _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]))
       hidden = down.shape[2]
       # (whole 16-byte groups per row, so that an expert's slice of the rows starts on a boundary)
-      if (gated and x.dtype == torch.bfloat16 and 0 < self.expert_rows_for_dense_products * num_experts <= pairs
+      if (x.dtype == torch.bfloat16 and 0 < self.expert_rows_for_dense_products * num_experts <= pairs
           and width % 8 == 0 and hidden % 8 == 0 and not torch.cuda.is_current_stream_capturing()):
-        y_pair = self._experts_one_by_one(x, sorted_pair, tiles, top, gate_up, down, activation)
+        y_pair = self._experts_one_by_one(x, sorted_pair, tiles, top, gate_up, down, activation, gated)
       else:
         h = self._new(pairs, hidden, dtype=x.dtype)
         self._call("sb_moe_product", _ptr(x), _ptr(sorted_pair), top, _ptr(gate_up), _code(x), int(gated), width, hidden,

@@ -303,6 +303,16 @@ def test_experts_by_table_with_equal_weights(sizes, where):
   got = ops.mix_experts(x, chosen, weight, up.contiguous(), down.contiguous(), experts, ACTIVATIONS.get("gelu_erf"),
                         None, None, gated=False)
   close(got.float().cpu().numpy(), want, dtype, f"experts {sizes}", f32=2e-5, bf16=3e-2)
+  if hasattr(ops, "expert_rows_for_dense_products"):
+    # both ways of multiplying: expert by expert through the dense products, and the grouped kernel
+    before = ops.expert_rows_for_dense_products
+    for threshold in (0, 1):
+      ops.expert_rows_for_dense_products = threshold
+      got = ops.mix_experts(x, chosen, weight, up.contiguous(), down.contiguous(), experts, ACTIVATIONS.get("gelu_erf"),
+                            None, None, gated=False)
+      close(got.float().cpu().numpy(), want, dtype, f"experts {sizes}, threshold {threshold}", f32=2e-5, bf16=3e-2)
+    ops.expert_rows_for_dense_products = before
+    ops.check_errors()
 
 
 # ---- one-layer models: every mixer alone at sizes of many kinds ------------------------------------------
