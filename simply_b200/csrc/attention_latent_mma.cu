@@ -56,6 +56,10 @@ struct LatentParams {
   const float* sink;   // [H] or null
   int num_heads, page_size, num_pages, window, num_seqs;
   int* err;
+  // With gridDim.y > 1 every tile's keys are split over that many blocks, which leave (max, sum) and
+  // unnormalised sums per row for `latent_combine_kernel`: part_ml [rows, splits, 2], part_o [rows, splits, VD].
+  float* part_ml;
+  float* part_o;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -230,6 +234,8 @@ __global__ void __launch_bounds__(WM * WN * NS * 32) latent_attention_kernel(con
   const int kv_hi = p1 + 1;
   const int tile0 = (lo / BN) * BN;
   const int n_tiles = (kv_hi - tile0 + BN - 1) / BN;
+  const int splits = gridDim.y, per_split = (n_tiles + splits - 1) / splits;
+  const int it_lo = blockIdx.y * per_split, it_hi = min(n_tiles, it_lo + per_split);  // this block's tiles
   // Brings keys [tile0 + it BN, + BN) to shared memory: first where each row lives (one block-table
   // lookup per row), then 16 bytes per thread and turn.  Contains one __syncthreads.
   auto load_tile = [&](int it, int stage) {
@@ -255,7 +261,7 @@ __global__ void __launch_bounds__(WM * WN * NS * 32) latent_attention_kernel(con
       cp_async16(dst + row * PITCH + c * 8, p.cache + (valid ? src : 0) + c * 8, valid);
     }
   };
-  load_tile(0, 0);
+  if (it_lo < it_hi) load_tile(it_lo, 0);
   cp_async_commit();
 
   const int ra = wm * 16 + g, rb = ra + 8;
@@ -269,9 +275,9 @@ __global__ void __launch_bounds__(WM * WN * NS * 32) latent_attention_kernel(con
 #pragma unroll
   for (int d = 0; d < VDS / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
-  for (int it = 0; it < n_tiles; ++it) {
-    const int stage = it & 1;
-    if (it + 1 < n_tiles) {
+  for (int it = it_lo; it < it_hi; ++it) {
+    const int stage = (it - it_lo) & 1;
+    if (it + 1 < it_hi) {
       load_tile(it + 1, stage ^ 1);
       cp_async_commit();
       cp_async_wait<1>();
@@ -289,6 +295,7 @@ __global__ void __launch_bounds__(WM * WN * NS * 32) latent_attention_kernel(con
                     vs * VDS, need_mask);
     __syncthreads();
   }
+  cp_async_wait<0>();  // (a block without tiles of its own still has its query rows under way)
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
@@ -337,6 +344,24 @@ __global__ void __launch_bounds__(WM * WN * NS * 32) latent_attention_kernel(con
     }
     if (wn != 0) return;
   }
+  if (splits > 1) {
+    // this block's part of every row; the sink and the division wait for the combine
+    if (ra < rows_valid) {
+      const size_t at = (first_row + ra) * splits + blockIdx.y;
+      if (t == 0 && vs == 0) { p.part_ml[2 * at] = m_a; p.part_ml[2 * at + 1] = l_a; }
+#pragma unroll
+      for (int d = 0; d < VDS / 8; ++d)
+        *reinterpret_cast<float2*>(p.part_o + at * VD + vs * VDS + d * 8 + 2 * t) = make_float2(o[d][0], o[d][1]);
+    }
+    if (rb < rows_valid) {
+      const size_t at = (first_row + rb) * splits + blockIdx.y;
+      if (t == 0 && vs == 0) { p.part_ml[2 * at] = m_b; p.part_ml[2 * at + 1] = l_b; }
+#pragma unroll
+      for (int d = 0; d < VDS / 8; ++d)
+        *reinterpret_cast<float2*>(p.part_o + at * VD + vs * VDS + d * 8 + 2 * t) = make_float2(o[d][2], o[d][3]);
+    }
+    return;
+  }
   if (p.sink != nullptr) {
     // exp(sink_h) joins the sum; it has no value, so the result only shrinks
     const float ka = p.sink[(r0 + min(ra, rows_valid - 1)) % H] * LOG2E, kb = p.sink[(r0 + min(rb, rows_valid - 1)) % H] * LOG2E;
@@ -367,8 +392,38 @@ __global__ void __launch_bounds__(WM * WN * NS * 32) latent_attention_kernel(con
   }
 }
 
+// Merges the parts of a row's key splits in their order, adds the sink to the sum and divides.
+constexpr int MAX_SPLITS = 16;
+__global__ void __launch_bounds__(128) latent_combine_kernel(const float* __restrict__ part_ml,
+                                                             const float* __restrict__ part_o, const float* __restrict__ sink,
+                                                             bf16* __restrict__ out, int num_heads, int splits) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t row = blockIdx.x;
+  float m_all = sink != nullptr ? sink[row % num_heads] * LOG2E : -INFINITY;
+  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, part_ml[2 * (row * splits + s)]);
+  float scale[MAX_SPLITS], l_all = sink != nullptr ? fast_exp2(sink[row % num_heads] * LOG2E - m_all) : 0.f;
+#pragma unroll
+  for (int s = 0; s < MAX_SPLITS; ++s) {
+    scale[s] = 0.f;
+    if (s < splits) {
+      const float m = part_ml[2 * (row * splits + s)];
+      scale[s] = m == -INFINITY ? 0.f : fast_exp2(m - m_all);
+      l_all += part_ml[2 * (row * splits + s) + 1] * scale[s];
+    }
+  }
+  const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+  for (int c = threadIdx.x; c < VD; c += blockDim.x) {
+    float sum = 0.f;
+#pragma unroll
+    for (int s = 0; s < MAX_SPLITS; ++s)
+      if (s < splits) sum = fmaf(part_o[(row * splits + s) * VD + c], scale[s], sum);
+    out[row * VD + c] = __float2bfloat16(sum * inv);
+  }
+}
+
 template <int WM, int WN, int BN>
-int launch(const LatentParams& p, int num_tokens, cudaStream_t stream) {
+int launch(const LatentParams& p, int num_tokens, int splits, cudaStream_t stream) {
   constexpr int BM = WM * 16;
   const size_t smem = (size_t)(BM + 2 * BN) * PITCH * sizeof(bf16);
   static bool configured = false;
@@ -380,8 +435,13 @@ int launch(const LatentParams& p, int num_tokens, cudaStream_t stream) {
   }
   const long long tiles = ((long long)num_tokens * p.num_heads + BM - 1) / BM + p.num_seqs;
   if (tiles > 0x7fffffffLL) return -6;
-  sb_launch(latent_attention_kernel<WM, WN, BN>, dim3((unsigned)tiles), WM * WN * NS * 32, smem, stream, p);
+  sb_launch(latent_attention_kernel<WM, WN, BN>, dim3((unsigned)tiles, (unsigned)splits), WM * WN * NS * 32, smem, stream, p);
   SB_LAUNCH_CHECK();
+  if (splits > 1) {
+    sb_launch(latent_combine_kernel, dim3((unsigned)(num_tokens * p.num_heads)), 128, 0, stream, (const float*)p.part_ml,
+              (const float*)p.part_o, p.sink, p.out, p.num_heads, splits);
+    SB_LAUNCH_CHECK();
+  }
   return 0;
 }
 
@@ -391,18 +451,22 @@ int launch(const LatentParams& p, int num_tokens, cudaStream_t stream) {
 #define SB_CAT5(a, b, c, d, e) SB_CAT5_(a, b, c, d, e)
 
 // q [T, H, KD] scaled, cache [P, page, KD], out [T, H * VD]; `max_q_len`: the longest portion of the step.
+// `splits` > 1 (steps of few rows per sequence only): every tile's keys over that many blocks, with
+// part_ml [T H, splits, 2] and part_o [T H, splits, VD] float32 as their meeting place.
 extern "C" int SB_CAT5(sb_latent_attention_k, SB_LATENT_KD, _v, SB_LATENT_VD, )(
     const void* q, const void* cache, const int* block_table, int max_pages, const int* cu_q, const int* q_start,
     void* out, const float* sink, int num_tokens, int num_seqs, int max_q_len, int num_heads, int page_size,
-    int num_pages, int window, int* err, cudaStream_t stream) {
+    int num_pages, int window, int splits, float* part_ml, float* part_o, int* err, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
-  if (num_heads <= 0 || num_seqs <= 0 || page_size <= 0) return -8;
+  if (num_heads <= 0 || num_seqs <= 0 || page_size <= 0 || splits < 1 || splits > MAX_SPLITS) return -8;
+  if (splits > 1 && (part_ml == nullptr || part_o == nullptr)) return -8;
   LatentParams p{};
   p.q = (const bf16*)q; p.cache = (const bf16*)cache; p.block_table = block_table; p.max_pages = max_pages;
   p.cu_q = cu_q; p.q_start = q_start; p.out = (bf16*)out; p.sink = sink; p.num_heads = num_heads;
   p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.num_seqs = num_seqs; p.err = err;
+  p.part_ml = part_ml; p.part_o = part_o;
   const long long rows = (long long)max_q_len * num_heads;
-  if (rows <= 16) return launch<1, 4, 64>(p, num_tokens, stream);
-  if (rows <= 32) return launch<2, 2, BN_WIDE>(p, num_tokens, stream);
-  return launch<4, 1, BN_WIDE>(p, num_tokens, stream);
+  if (rows <= 16) return launch<1, 4, 64>(p, num_tokens, splits, stream);
+  if (rows <= 32) return launch<2, 2, BN_WIDE>(p, num_tokens, splits, stream);
+  return launch<4, 1, BN_WIDE>(p, num_tokens, splits, stream);
 }

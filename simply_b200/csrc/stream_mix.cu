@@ -9,6 +9,8 @@
 //   group norm with a gate     per token, N numbers in equal groups, each divided by its root mean
 //                              square, times w; a gate as silu before or as sigmoid after
 //   tanh of a column range, experts by a table of token ids, a product per head
+#include <type_traits>
+
 #include "common.cuh"
 
 #define SB_ERR_BAD_SLOT 16    // a state slot outside the state tensor
@@ -88,7 +90,8 @@ extern "C" int sb_spread_streams(const float* h, float* lanes, int num_tokens, i
 
 // ---------------------------------------------------------------------------
 // One block per row.  With `rows`, block r works on row rows[r], writes y[r] and leaves the lanes.
-template <typename T>
+// S_: the number of copies where the launch knows it at compile time (1 to 4), else 0.
+template <typename T, int S_>
 __global__ void streams_step_kernel(float* __restrict__ lanes, const T* __restrict__ branch,
                                     const float* __restrict__ mix, const float* __restrict__ out_w,
                                     const float* __restrict__ in_w, const void* __restrict__ norm_w, int norm_f32,
@@ -105,6 +108,8 @@ __global__ void streams_step_kernel(float* __restrict__ lanes, const T* __restri
   }
   pdl_wait_block();
   pdl_launch_dependents();
+  constexpr int MAXS = S_ > 0 ? S_ : SB_MAX_STREAMS;
+  if (S_ > 0) copies = S_;
   int r = blockIdx.x;
   if (rows != nullptr) {
     r = rows[blockIdx.x];
@@ -115,35 +120,70 @@ __global__ void streams_step_kernel(float* __restrict__ lanes, const T* __restri
   }
   float* x = lanes + (size_t)r * copies * width;
   float sq = 0.f;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    float old[SB_MAX_STREAMS], now[SB_MAX_STREAMS];
+  // V neighbouring columns per thread and turn, every copy's V values fetched at once (16 bytes when
+  // the width allows) before anything is written: a row's columns are a few turns of independent
+  // fetches, not a chain of fetch, compute, store per column.
+  auto columns = [&](auto vtag, int c) {
+    constexpr int V = decltype(vtag)::value;
+    float old[MAXS][V], now[MAXS][V], b[V];
 #pragma unroll
-    for (int s = 0; s < SB_MAX_STREAMS; ++s) old[s] = s < copies ? x[(size_t)s * width + c] : 0.f;
+    for (int s = 0; s < MAXS; ++s) {
+      if (s < copies) {
+        if constexpr (V == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(x + (size_t)s * width + c);
+          old[s][0] = v.x; old[s][1] = v.y; old[s][2] = v.z; old[s][3] = v.w;
+        } else {
+          old[s][0] = x[(size_t)s * width + c];
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) old[s][e] = 0.f;
+      }
+    }
     if (branch != nullptr) {
-      const float b = to_f32<T>(branch[(size_t)r * width + c]);
 #pragma unroll
-      for (int t = 0; t < SB_MAX_STREAMS; ++t) {
+      for (int e = 0; e < V; ++e) b[e] = to_f32<T>(branch[(size_t)r * width + c + e]);
+#pragma unroll
+      for (int t = 0; t < MAXS; ++t) {
         if (t < copies) {
-          float acc = 0.f;
 #pragma unroll
-          for (int s = 0; s < SB_MAX_STREAMS; ++s)
-            if (s < copies) acc = fmaf(s_mix[s * copies + t], old[s], acc);
-          now[t] = fmaf(s_out[t], b, acc);
-          if (rows == nullptr) x[(size_t)t * width + c] = now[t];
+          for (int e = 0; e < V; ++e) {
+            float acc = 0.f;
+#pragma unroll
+            for (int s = 0; s < MAXS; ++s)
+              if (s < copies) acc = fmaf(s_mix[s * copies + t], old[s][e], acc);
+            now[t][e] = fmaf(s_out[t], b[e], acc);
+          }
+          if (rows == nullptr) {
+            if constexpr (V == 4)
+              *reinterpret_cast<float4*>(x + (size_t)t * width + c) = make_float4(now[t][0], now[t][1], now[t][2], now[t][3]);
+            else
+              x[(size_t)t * width + c] = now[t][0];
+          }
         }
       }
     } else {
 #pragma unroll
-      for (int s = 0; s < SB_MAX_STREAMS; ++s) now[s] = old[s];
+      for (int s = 0; s < MAXS; ++s)
+#pragma unroll
+        for (int e = 0; e < V; ++e) now[s][e] = old[s][e];
     }
     if (in_w != nullptr) {
-      float u = 0.f;
 #pragma unroll
-      for (int s = 0; s < SB_MAX_STREAMS; ++s)
-        if (s < copies) u = fmaf(s_in[s], now[s], u);
-      row[c] = u;
-      sq = fmaf(u, u, sq);
+      for (int e = 0; e < V; ++e) {
+        float u = 0.f;
+#pragma unroll
+        for (int s = 0; s < MAXS; ++s)
+          if (s < copies) u = fmaf(s_in[s], now[s][e], u);
+        row[c + e] = u;
+        sq = fmaf(u, u, sq);
+      }
     }
+  };
+  if (S_ > 0 && (width & 3) == 0) {
+    for (int c = threadIdx.x * 4; c < width; c += blockDim.x * 4) columns(std::integral_constant<int, 4>{}, c);
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) columns(std::integral_constant<int, 1>{}, c);
   }
   if (in_w == nullptr) return;
   if (norm_w == nullptr) {
@@ -168,15 +208,26 @@ extern "C" int sb_streams_step(float* lanes, const void* branch, int dtype, cons
   const size_t smem = ((size_t)width + 33) * sizeof(float);
   if (smem > 200 * 1024) return -13;
   const int threads = width >= 1024 ? 256 : 128;
-#define SB_STREAMS(T_)                                                                                           \
+#define SB_STREAMS(T_, S__)                                                                                           \
   do {                                                                                                           \
     if (smem > 48 * 1024)                                                                                        \
-      cudaFuncSetAttribute(streams_step_kernel<T_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-    sb_launch(streams_step_kernel<T_>, num_rows, threads, smem, stream, lanes, (const T_*)branch, mix, out_w,    \
+      cudaFuncSetAttribute(streams_step_kernel<T_, S__>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    sb_launch(streams_step_kernel<T_, S__>, num_rows, threads, smem, stream, lanes, (const T_*)branch, mix, out_w, \
               in_w, norm_w, norm_f32, eps, plus_one, rows, (T_*)y, y_sum, copies, width, num_rows_total, err);   \
   } while (0)
-  if (dtype == SB_DTYPE_F32) SB_STREAMS(float);
-  else SB_STREAMS(bf16);
+#define SB_STREAMS_OF(S__)                       \
+  do {                                           \
+    if (dtype == SB_DTYPE_F32) SB_STREAMS(float, S__); \
+    else SB_STREAMS(bf16, S__);                  \
+  } while (0)
+  switch (copies) {
+    case 1: SB_STREAMS_OF(1); break;
+    case 2: SB_STREAMS_OF(2); break;
+    case 3: SB_STREAMS_OF(3); break;
+    case 4: SB_STREAMS_OF(4); break;
+    default: SB_STREAMS_OF(0); break;
+  }
+#undef SB_STREAMS_OF
 #undef SB_STREAMS
   SB_LAUNCH_CHECK();
   return 0;

@@ -354,8 +354,8 @@ class CudaOps:
   def _library_head_products(self, x: torch.Tensor, x_head: int, w: torch.Tensor, out: torch.Tensor, out_head: int,
                              alpha: float) -> bool:
     """out[:, h * out_head : + N] = alpha * x[:, h * x_head : + K] . w[h]^T for w [H, N, K], all heads in one
-    call of the matrix-product library (bfloat16, from 17 rows); False when it does not take the shape."""
-    if x.dtype != torch.bfloat16 or x.shape[0] <= self.skinny_max_rows or not self.direct_library_products:
+    call of the matrix-product library (bfloat16); False when it does not take the shape."""
+    if x.dtype != torch.bfloat16 or not self.direct_library_products:
       return False
     stream = self._stream()
     workspace = self._library_workspaces.get(stream.value)
@@ -450,7 +450,7 @@ class CudaOps:
       c_int, c_void = ctypes.c_int, ctypes.c_void_p
       fn = getattr(lib, f"sb_latent_attention_k{row_dim}_v{value_dim}")
       fn.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
-                     c_int, c_int, c_void, c_void]
+                     c_int, c_int, c_int, c_void, c_void, c_void, c_void]
       fn.restype = c_int
       self._latent_fns[(row_dim, value_dim)] = fn
     return fn
@@ -913,11 +913,20 @@ class CudaOps:
       if (values_in_keys and pooled is None and num_kv_heads == 1 and q.dtype == torch.bfloat16
           and self.tensor_core_attention and build.latent_shape_ok(head_dim, value_dim)):
         # a cache of latents in bfloat16: the tensor-core kernel of this shape (csrc/attention_latent_mma.cu)
+        # Steps of few rows per sequence (single tokens): every sequence's keys are split over several
+        # blocks, by what a sequence can hold (not by what it holds now: a captured graph keeps the launch).
+        splits, part_ml, part_o = 1, None, None
+        if ctx.max_q_len * num_heads <= 32 and t * num_heads <= 8192:
+          reach = min(int(window or (1 << 30)), block_table.shape[1] * ctx.page_size)
+          splits = max(1, min(16, reach // 128))
+        if splits > 1:
+          part_ml = self._new(t * num_heads * splits * 2, dtype=torch.float32)
+          part_o = self._new(t * num_heads * splits * value_dim, dtype=torch.float32)
         rc = self._latent_fn(head_dim, value_dim)(
             _ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_q), _ptr(ctx.q_start),
             _ptr(out), _ptr(sink), t, ctx.num_seqs, ctx.max_q_len, num_heads, ctx.page_size, storage.shape[0],
-            int(window or 0), _ptr(self.err), self._stream())
-        self.launches += 1
+            int(window or 0), splits, _ptr(part_ml), _ptr(part_o), _ptr(self.err), self._stream())
+        self.launches += 1 + (splits > 1)
         if rc:
           raise KernelError(f"sb_latent_attention: {_STATUS.get(rc, rc)}")
         return out
