@@ -273,3 +273,15 @@ def test_decoding_from_graphs_equals_decoding_step_by_step(dtype):
     outs.append([list(r.output_token_ids) for r in results])
     engine.ops.check_errors()
   assert outs[0] == outs[1]
+
+
+def test_the_preset_generates_from_random_weights():
+  from simply_b200.config import preset
+  cfg = preset("zesapel-tiny")
+  assert cfg.architecture == "Zesapel" and cfg.streams == 2 and cfg.canon_taps == 3
+  kinds = [layer.mixer.kind for layer in cfg.model_spec().layers]
+  assert kinds == ["latent_attention", "generalized_delta_rule", "state_space_duality"]
+  ec = EngineConfig(activation_dtype="float32", page_size=8, batch_size=2, max_seq_len=64, use_cuda_graphs=False)
+  engine = Engine.from_config(cfg, 1, ec, matrix_std=0.2, ops=ReferenceOps(torch.float32), device="cpu")
+  results = engine.generate([[1, 2, 3], [7]], SamplingParams(temperature=0.0, max_decode_steps=5))
+  assert [len(r.output_token_ids) for r in results] == [5, 5]
