@@ -401,6 +401,122 @@ state_space_scan_kernel(const float* __restrict__ xbc, int C, const float* __res
   }
 }
 
+// The same walk with a patch of the state per lane: 4 neighbouring rows x 4 neighbouring columns, so a
+// fetched element of B, C or x serves four multiply-adds (the column-per-lanes layout above fetches one
+// per multiply-add, and its instructions, not memory, bound a long walk).  RG lanes (a power of two, 4 to
+// 32) stand side by side over the rows, 32 / RG groups of four columns per warp.  The four sums of a lane
+// meet over the RG lanes in a butterfly that halves what is passed on in its first two steps.  State sizes
+// 16 to 128; rows and columns beyond the state's stay zero (their B, C and x are zero in shared memory).
+template <int RG>
+__global__ void __launch_bounds__(128)
+state_space_patch_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ steps,
+                         const float* __restrict__ skip, float* __restrict__ state, const int* __restrict__ cu_q,
+                         const int* __restrict__ slots, int num_slots, int H, int G, int N, int dv, int chunk,
+                         float* __restrict__ out, int* err) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  constexpr int CG = 32 / RG, NP = RG * 4;       // column groups per warp; rows a warp spans
+  extern __shared__ __align__(16) float stage[];  // two buffers of chunk x (B: NP | C: NP | x: cols | 4)
+  const int warps = blockDim.x >> 5, cols = warps * CG * 4;
+  const int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * cols;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rg = lane % RG, cg = warp * CG + lane / RG;
+  const int row_first = rg * 4, col_local = cg * 4, col_first = col0 + col_local;
+  const int first = cu_q[b], n = cu_q[b + 1] - first;
+  const int slot = slots[b];
+  if (slot < 0 || slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_SLOT);
+    return;
+  }
+  const int g = h / (H / G);
+  const int inner = H * dv;
+  const int per_token = 2 * NP + cols + 4;
+  const bool wide = (N & 3) == 0 && (C & 3) == 0 && (inner & 3) == 0;
+  const int cols_here = min(cols, dv - col0);
+  const float d_skip = skip[h];
+  // what no copy ever writes stays zero: rows from N on, columns from the head's last on
+  for (int i = threadIdx.x; i < 2 * chunk * per_token; i += blockDim.x) stage[i] = 0.f;
+  __syncthreads();
+
+  auto issue = [&](int which, int base) {
+    float* buf = stage + (size_t)which * chunk * per_token;
+    const int count = min(chunk, n - base);
+    for (int i = 0; i < count; ++i) {
+      const float* row = xbc + (size_t)(first + base + i) * C;
+      float* dst = buf + (size_t)i * per_token;
+      stage_row(dst, row + inner + (size_t)g * N, N, wide);
+      stage_row(dst + NP, row + inner + (size_t)(G + g) * N, N, wide);
+      for (int c = threadIdx.x; c < cols_here; c += blockDim.x) stage4(dst + 2 * NP + c, row + (size_t)h * dv + col0 + c);
+      if (threadIdx.x < 2)
+        stage4(dst + 2 * NP + cols + threadIdx.x, steps + ((size_t)(first + base + i) * H + h) * 2 + threadIdx.x);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+
+  if (n > 0) issue(0, 0);
+  float* S = state + ((size_t)slot * H + h) * N * dv;
+  float s[4][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      s[r][q] = (row_first + r < N && col_first + q < dv) ? S[(size_t)(row_first + r) * dv + col_first + q] : 0.f;
+  const bool low1 = rg & 1, low2 = rg & 2;
+  int which = 0;
+  for (int base = 0; base < n; base += chunk, which ^= 1) {
+    const int count = min(chunk, n - base);
+    if (base + chunk < n) {
+      issue(which ^ 1, base + chunk);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
+    __syncthreads();
+    const float* buf = stage + (size_t)which * chunk * per_token;
+#pragma unroll 2
+    for (int i = 0; i < count; ++i) {
+      const float* tok = buf + (size_t)i * per_token;
+      const float4 bv = *reinterpret_cast<const float4*>(tok + row_first);
+      const float4 cv = *reinterpret_cast<const float4*>(tok + NP + row_first);
+      const float4 xv = *reinterpret_cast<const float4*>(tok + 2 * NP + col_local);
+      const float decay = tok[2 * NP + cols], dt = tok[2 * NP + cols + 1];
+      const float bm[4] = {bv.x, bv.y, bv.z, bv.w}, cm[4] = {cv.x, cv.y, cv.z, cv.w};
+      const float x[4] = {xv.x, xv.y, xv.z, xv.w};
+      float y[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float push = dt * x[q];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          s[r][q] = fmaf(push, bm[r], decay * s[r][q]);
+          y[q] = fmaf(s[r][q], cm[r], y[q]);
+        }
+      }
+      // lanes with an odd rg go on with columns 2, 3, the others with 0, 1; then one column each
+      const float t0 = __shfl_xor_sync(0xffffffffu, low1 ? y[0] : y[2], 1);
+      const float t1 = __shfl_xor_sync(0xffffffffu, low1 ? y[1] : y[3], 1);
+      const float a0 = (low1 ? y[2] : y[0]) + t0, a1 = (low1 ? y[3] : y[1]) + t1;
+      const float t2 = __shfl_xor_sync(0xffffffffu, low2 ? a0 : a1, 2);
+      float v = (low2 ? a1 : a0) + t2;
+#pragma unroll
+      for (int o = 4; o < RG; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      const int q_mine = (low1 ? 2 : 0) + (low2 ? 1 : 0);
+      if (rg < 4 && col_first + q_mine < dv) {
+        const float xq = low1 ? (low2 ? x[3] : x[2]) : (low2 ? x[1] : x[0]);
+        out[((size_t)(first + base + i) * H + h) * dv + col_first + q_mine] = fmaf(d_skip, xq, v);
+      }
+    }
+    __syncthreads();
+  }
+  if (owns_slot(slots, b)) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (row_first + r < N && col_first + q < dv) S[(size_t)(row_first + r) * dv + col_first + q] = s[r][q];
+  }
+}
+
 // scratch: float32 [T, H, 2].
 extern "C" int sb_state_space_scan(const float* xbc, int C, const void* pre, int pre_width, int dtype,
                                    int step_offset, const float* step_bias, const float* neg_rate,
@@ -418,10 +534,34 @@ extern "C" int sb_state_space_scan(const float* xbc, int C, const void* pre, int
     sb_launch(state_space_steps_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)pre, pre_width, step_offset,
               step_bias, neg_rate, H, total, scratch);
   SB_LAUNCH_CHECK();
+  const bool long_walk = max_q_len >= 64;
+  if (long_walk && N >= 16 && N <= 128) {
+    int rg = 4;
+    while (rg * 4 < N) rg <<= 1;
+    int chunk = 16;
+    const int warps = 4, cols = warps * (32 / rg) * 4;
+    const dim3 grid(H, num_seqs, (dv + cols - 1) / cols);
+    const size_t smem = (size_t)2 * chunk * (2 * rg * 4 + cols + 4) * sizeof(float);
+#define SB_SS_PATCH(RG_)                                                                                       \
+  do {                                                                                                         \
+    if (smem > 48 * 1024)                                                                                      \
+      cudaFuncSetAttribute(state_space_patch_kernel<RG_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    sb_launch_plain(state_space_patch_kernel<RG_>, grid, warps * 32, smem, stream, xbc, C, scratch, skip, state, \
+                    cu_q, slots, num_slots, H, G, N, dv, chunk, out, err);                                     \
+  } while (0)
+    switch (rg) {
+      case 4: SB_SS_PATCH(4); break;
+      case 8: SB_SS_PATCH(8); break;
+      case 16: SB_SS_PATCH(16); break;
+      default: SB_SS_PATCH(32); break;
+    }
+#undef SB_SS_PATCH
+    SB_LAUNCH_CHECK();
+    return 0;
+  }
   const int rows = N <= 256 ? 8 : 32;
   int rs = 1;
   while (rs * rows < N) rs <<= 1;
-  const bool long_walk = max_q_len >= 64;
   const int threads = long_walk ? 128 : 64;
   int chunk = 1;
   while (chunk < 16 && chunk < max_q_len) chunk <<= 1;

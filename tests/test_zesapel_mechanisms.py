@@ -131,7 +131,8 @@ def test_the_delta_walk_carries_its_state_between_steps(sizes, where):
 
 @pytest.mark.parametrize("where", WHERE)
 @pytest.mark.parametrize("sizes", [(4, 6, 10, 2), (2, 16, 8, 1), (3, 8, 4, 3), (4, 64, 128, 2), (1, 3, 300, 1),
-                                   (6, 1, 1, 3), (3, 5, 7, 1)])
+                                   (6, 1, 1, 3), (3, 5, 7, 1), (3, 5, 20, 1), (2, 40, 64, 2), (5, 16, 16, 1),
+                                   (2, 24, 100, 1)])
 def test_the_state_space_walk_carries_its_state_between_steps(sizes, where):
   heads, dv, n, groups = sizes
   ops, dtype = table(where)
