@@ -116,9 +116,41 @@ general_delta_scan_kernel(const float* __restrict__ vecs, const float* __restric
   const int per_token = 5 * d + cols_pad + 4;
   const bool wide = (d & 3) == 0;
 
+  // Staging a chunk, where rows are whole 16-byte groups: a thread takes a piece of a token (16 bytes of
+  // the five vectors, one value, one of the two dot products) and copies it for every token of the
+  // chunk, one copy and two additions per token; all threads walking every token's rows in turn cost more
+  // instructions than the walk itself.
+  const int vec_pieces = (5 * d) >> 2, pieces = vec_pieces + cols + 2;
+  auto issue_pieces = [&](float* buf, int base, int count) {
+    for (int k = threadIdx.x; k < pieces; k += blockDim.x) {
+      const float* src;
+      size_t stride;
+      int dst_off;
+      const bool sixteen = k < vec_pieces;
+      if (sixteen) {
+        src = vecs + ((size_t)(first + base) * H + h) * 5 * d + 4 * k; stride = (size_t)H * 5 * d; dst_off = 4 * k;
+      } else if (k < vec_pieces + cols) {
+        const int c = k - vec_pieces;
+        src = vals + ((size_t)(first + base) * H + h) * d + min(col0 + c, d - 1); stride = (size_t)H * d; dst_off = 5 * d + c;
+      } else {
+        const int j = k - vec_pieces - cols;
+        src = dots + ((size_t)(first + base) * H + h) * 2 + j; stride = (size_t)2 * H; dst_off = 5 * d + cols_pad + j;
+      }
+      float* dst = buf + dst_off;
+      for (int i = 0; i < count; ++i, src += stride, dst += per_token) {
+        if (sixteen) stage16(dst, src);
+        else stage4(dst, src);
+      }
+    }
+  };
   auto issue = [&](int which, int base) {
     float* buf = stage + (size_t)which * chunk * per_token;
     const int count = min(chunk, n - base);
+    if (wide) {
+      issue_pieces(buf, base, count);
+      asm volatile("cp.async.commit_group;\n" ::);
+      return;
+    }
     for (int i = 0; i < count; ++i) {
       const size_t at = (size_t)(first + base + i) * H + h;
       float* dst = buf + (size_t)i * per_token;
@@ -438,9 +470,44 @@ state_space_patch_kernel(const float* __restrict__ xbc, int C, const float* __re
   for (int i = threadIdx.x; i < 2 * chunk * per_token; i += blockDim.x) stage[i] = 0.f;
   __syncthreads();
 
+  // Staging a chunk: where every piece of a token fits one thread (16 bytes of B or C, one x, one step
+  // value), a thread copies its piece of every token of the chunk, one copy and two additions per token;
+  // otherwise the threads share out every token's rows in turn.
+  const int nb = N >> 2;
+  const bool piecewise = wide && 2 * nb + cols_here + 2 <= (int)blockDim.x;
+  const float* piece_src = nullptr;
+  size_t piece_stride = 0;
+  int piece_dst = 0;
+  bool piece16 = false;
+  {
+    const int k = threadIdx.x;
+    if (k < nb) {
+      piece_src = xbc + (size_t)first * C + inner + (size_t)g * N + 4 * k; piece_stride = C; piece_dst = 4 * k; piece16 = true;
+    } else if (k < 2 * nb) {
+      piece_src = xbc + (size_t)first * C + inner + (size_t)(G + g) * N + 4 * (k - nb); piece_stride = C;
+      piece_dst = NP + 4 * (k - nb); piece16 = true;
+    } else if (k < 2 * nb + cols_here) {
+      piece_src = xbc + (size_t)first * C + (size_t)h * dv + col0 + (k - 2 * nb); piece_stride = C; piece_dst = 2 * NP + (k - 2 * nb);
+    } else if (k < 2 * nb + cols_here + 2) {
+      const int j = k - 2 * nb - cols_here;
+      piece_src = steps + ((size_t)first * H + h) * 2 + j; piece_stride = (size_t)2 * H; piece_dst = 2 * NP + cols + j;
+    }
+  }
   auto issue = [&](int which, int base) {
     float* buf = stage + (size_t)which * chunk * per_token;
     const int count = min(chunk, n - base);
+    if (piecewise) {
+      if (piece_src != nullptr) {
+        const float* src = piece_src + (size_t)base * piece_stride;
+        float* dst = buf + piece_dst;
+        for (int i = 0; i < count; ++i, src += piece_stride, dst += per_token) {
+          if (piece16) stage16(dst, src);
+          else stage4(dst, src);
+        }
+      }
+      asm volatile("cp.async.commit_group;\n" ::);
+      return;
+    }
     for (int i = 0; i < count; ++i) {
       const float* row = xbc + (size_t)(first + base + i) * C;
       float* dst = buf + (size_t)i * per_token;
