@@ -208,7 +208,9 @@ extern "C" int sb_gemm_library_bf16_heads(const void* x, int x_stride, int x_hea
       const float beta = 0.0f;
       cublasStatus_t st = api->matmul(api->handle, api->op, &alpha, w, l.a, x, l.b, &beta, out, l.c, out, l.c,
                                       &it->second.algo, workspace, it->second.workspace, stream);
-      rc = st == CUBLAS_STATUS_SUCCESS ? 0 : (st == CUBLAS_STATUS_NOT_SUPPORTED ? -9 : (int)st);
+      // (a shape the library refuses goes to the caller's own kernel; only a failed run is an error)
+      rc = st == CUBLAS_STATUS_SUCCESS ? 0
+           : (st == CUBLAS_STATUS_NOT_SUPPORTED || st == CUBLAS_STATUS_INVALID_VALUE) ? -9 : (int)st;
     }
   }
   drop_layouts(api, l);
