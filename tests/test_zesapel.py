@@ -101,9 +101,9 @@ def test_larger_sizes_and_pages_of_64(dtype):
   states of 64 and 128 rows, two groups, a token with two experts."""
   cfg_dict = zc.config(
       [zc.latent(heads=8, dim=32, rot_dim=16, vdim=32, q_rank=48, kv_rank=64, dims=16, base=5000.0, scale=0.15, window=50),
-       zc.delta(heads=2, dim=64),
+       zc.delta(heads=3, dim=64),
        zc.mamba(heads=4, vdim=32, state=64, groups=2, norm_groups=2, conv=4),
-       zc.latent(heads=4, dim=64, rot_dim=32, vdim=64, q_rank=96, kv_rank=96, dims=8, base=100.0, scale=0.1, window=130),
+       zc.latent(heads=6, dim=48, rot_dim=32, vdim=32, q_rank=72, kv_rank=128, dims=8, base=100.0, scale=0.1, window=130),
        zc.delta(heads=1, dim=128)],
       [zc.moe(experts=8, top=2, ff=64), zc.moe(experts=3, top=1, ff=128), None, zc.moe(experts=5, top=3, ff=32),
        zc.moe(experts=4, top=2, ff=64)],

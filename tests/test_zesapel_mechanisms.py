@@ -372,3 +372,22 @@ def test_the_sink_takes_its_share_and_the_gate_scales_heads(where):
     seen.append(want)
   assert np.abs(seen[0] - seen[1]).max() > 0.05 * np.abs(seen[0]).max()
   assert np.abs(seen[0] - seen[2]).max() > 0.05 * np.abs(seen[0]).max()
+
+
+@pytest.mark.parametrize("where", WHERE)
+def test_one_tap_on_the_input_and_four_streams(where):
+  """Values that other tests leave out: a convolution of a single tap (no kept inputs at all) on what the
+  mixer reads, four streams, a window as long as the sequence."""
+  dtype, device = where
+  cfg_dict = zc.config([zc.delta(heads=2, dim=8), zc.latent(heads=2, dim=8, rot_dim=8, vdim=8, q_rank=8, kv_rank=8, dims=8, window=45),
+                        zc.mamba(heads=2, vdim=8, state=16, groups=1, norm_groups=1, conv=2)],
+                       [zc.moe(experts=2, top=1, ff=8), None, zc.moe(experts=4, top=4, ff=8)], width=24, vocab=41, streams=4,
+                       taps=1, rank=2)
+  cfg, t = zc.weights(cfg_dict, seed=13)
+  ops = ReferenceOps(torch.float32) if device == "cpu" else None
+  engine = zc.build_engine(cfg, t, dtype, device, ops, page_size=4)
+  toks = np.random.default_rng(3).integers(0, 41, 45).tolist()
+  want = plain.forward(cfg_dict, zc.as_numpy(t), toks)
+  for what, cuts in [("whole", [45]), ("decoded", [20] + [1] * 25), ("portions", zc.cuts_of(45, [3, 2, 9, 2, 14]))]:
+    zc.check_close(zc.run_cuts(engine, toks, cuts), want, dtype, what)
+  engine.ops.check_errors()
