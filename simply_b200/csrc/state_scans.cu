@@ -252,6 +252,142 @@ general_delta_scan_kernel(const float* __restrict__ vecs, const float* __restric
   }
 }
 
+// The delta rule's walk with a patch of the state per lane (4 rows x 4 columns), for prompt portions
+// with heads of 16 to 128 channels in whole groups of four: a fetched element of a vector serves four
+// multiply-adds.  RG lanes (a power of two, 4 to 32) stand over the rows, 32 / RG groups of four
+// columns per warp.  The sums u^T S of a lane's four columns are needed by every lane of the group
+// before the update (a butterfly over the RG lanes); the sums for the output wait for nobody and meet in
+// a butterfly that halves what is passed on in its first two steps.
+template <int RG>
+__global__ void __launch_bounds__(128)
+general_delta_patch_kernel(const float* __restrict__ vecs, const float* __restrict__ vals,
+                           const float* __restrict__ dots, float* __restrict__ state, const int* __restrict__ cu_q,
+                           const int* __restrict__ slots, int num_slots, int H, int d, int chunk,
+                           float* __restrict__ out, int* err) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  constexpr int CG = 32 / RG, NP = RG * 4;
+  extern __shared__ __align__(16) float stage[];  // two buffers of chunk x (w, u, a u, k, r: NP each | v: cols | 4)
+  const int warps = blockDim.x >> 5, cols = warps * CG * 4;
+  const int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * cols;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rg = lane % RG, cg = warp * CG + lane / RG;
+  const int row_first = rg * 4, col_local = cg * 4, col_first = col0 + col_local;
+  const int first = cu_q[b], n = cu_q[b + 1] - first;
+  const int slot = slots[b];
+  if (slot < 0 || slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_SLOT);
+    return;
+  }
+  const int per_token = 5 * NP + cols + 4;
+  const int cols_here = max(0, min(cols, d - col0));
+  for (int i = threadIdx.x; i < 2 * chunk * per_token; i += blockDim.x) stage[i] = 0.f;  // rows and columns past d stay zero
+  __syncthreads();
+  const int d4 = d >> 2, vec_pieces = 5 * d4, pieces = vec_pieces + cols_here + 2;
+  auto issue = [&](int which, int base) {
+    float* buf = stage + (size_t)which * chunk * per_token;
+    const int count = min(chunk, n - base);
+    for (int k = threadIdx.x; k < pieces; k += blockDim.x) {
+      const float* src;
+      size_t stride;
+      int dst_off;
+      const bool sixteen = k < vec_pieces;
+      if (sixteen) {
+        const int j = k / d4, within = k - j * d4;
+        src = vecs + ((size_t)(first + base) * H + h) * 5 * d + (size_t)j * d + 4 * within; stride = (size_t)H * 5 * d;
+        dst_off = j * NP + 4 * within;
+      } else if (k < vec_pieces + cols_here) {
+        const int c = k - vec_pieces;
+        src = vals + ((size_t)(first + base) * H + h) * d + col0 + c; stride = (size_t)H * d; dst_off = 5 * NP + c;
+      } else {
+        const int j = k - vec_pieces - cols_here;
+        src = dots + ((size_t)(first + base) * H + h) * 2 + j; stride = (size_t)2 * H; dst_off = 5 * NP + cols + j;
+      }
+      float* dst = buf + dst_off;
+      for (int i = 0; i < count; ++i, src += stride, dst += per_token) {
+        if (sixteen) stage16(dst, src);
+        else stage4(dst, src);
+      }
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+
+  if (n > 0) issue(0, 0);
+  float* S = state + ((size_t)slot * H + h) * d * d;
+  float s[4][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      s[r][q] = (row_first + r < d && col_first + q < d) ? S[(size_t)(row_first + r) * d + col_first + q] : 0.f;
+  const bool low1 = rg & 1, low2 = rg & 2;
+  int which = 0;
+  for (int base = 0; base < n; base += chunk, which ^= 1) {
+    const int count = min(chunk, n - base);
+    if (base + chunk < n) {
+      issue(which ^ 1, base + chunk);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
+    __syncthreads();
+    const float* buf = stage + (size_t)which * chunk * per_token;
+#pragma unroll 2
+    for (int i = 0; i < count; ++i) {
+      const float* tok = buf + (size_t)i * per_token;
+      const float4 w4 = *reinterpret_cast<const float4*>(tok + row_first);
+      const float4 u4 = *reinterpret_cast<const float4*>(tok + NP + row_first);
+      const float4 a4 = *reinterpret_cast<const float4*>(tok + 2 * NP + row_first);
+      const float4 k4 = *reinterpret_cast<const float4*>(tok + 3 * NP + row_first);
+      const float4 r4 = *reinterpret_cast<const float4*>(tok + 4 * NP + row_first);
+      const float4 v4 = *reinterpret_cast<const float4*>(tok + 5 * NP + col_local);
+      const float ra = tok[5 * NP + cols], rk = tok[5 * NP + cols + 1];
+      const float w[4] = {w4.x, w4.y, w4.z, w4.w}, u[4] = {u4.x, u4.y, u4.z, u4.w}, au[4] = {a4.x, a4.y, a4.z, a4.w};
+      const float k[4] = {k4.x, k4.y, k4.z, k4.w}, rr[4] = {r4.x, r4.y, r4.z, r4.w}, v[4] = {v4.x, v4.y, v4.z, v4.w};
+      // one pass over the old state gives both sums: o = r . (w * s) - p (r . a u) + v (r . k)
+      float p[4] = {0.f, 0.f, 0.f, 0.f}, od[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          p[q] = fmaf(u[r], s[r][q], p[q]);
+          s[r][q] *= w[r];
+          od[q] = fmaf(rr[r], s[r][q], od[q]);
+        }
+#pragma unroll
+      for (int o = 1; o < RG; o <<= 1)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) p[q] += __shfl_xor_sync(0xffffffffu, p[q], o);
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) s[r][q] = fmaf(k[r], v[q], fmaf(-au[r], p[q], s[r][q]));
+      // lanes with an odd rg go on with columns 2, 3, the others with 0, 1; then one column each
+      const float t0 = __shfl_xor_sync(0xffffffffu, low1 ? od[0] : od[2], 1);
+      const float t1 = __shfl_xor_sync(0xffffffffu, low1 ? od[1] : od[3], 1);
+      const float a0 = (low1 ? od[2] : od[0]) + t0, a1 = (low1 ? od[3] : od[1]) + t1;
+      const float t2 = __shfl_xor_sync(0xffffffffu, low2 ? a0 : a1, 2);
+      float sum = (low2 ? a1 : a0) + t2;
+#pragma unroll
+      for (int o = 4; o < RG; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      const int q_mine = (low1 ? 2 : 0) + (low2 ? 1 : 0);
+      if (rg < 4 && col_first + q_mine < d) {
+        const float vq = low1 ? (low2 ? v[3] : v[2]) : (low2 ? v[1] : v[0]);
+        const float pq = low1 ? (low2 ? p[3] : p[2]) : (low2 ? p[1] : p[0]);
+        out[((size_t)(first + base + i) * H + h) * d + col_first + q_mine] = fmaf(vq, rk, fmaf(-pq, ra, sum));
+      }
+    }
+    __syncthreads();
+  }
+  if (owns_slot(slots, b)) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (row_first + r < d && col_first + q < d) S[(size_t)(row_first + r) * d + col_first + q] = s[r][q];
+  }
+}
+
 // scratch: float32 [T, H, 6 d + 2].
 extern "C" int sb_general_delta_scan(const void* pre, int pre_width, const void* low, int low_width, int dtype,
                                      const float* decay_bias, const float* removal_bias, float* state,
@@ -272,10 +408,33 @@ extern "C" int sb_general_delta_scan(const void* pre, int pre_width, const void*
     sb_launch(general_delta_inputs_kernel<bf16>, in_blocks, 256, 0, stream, (const bf16*)pre, pre_width,
               (const bf16*)low, low_width, decay_bias, removal_bias, H, d, num_tokens, vecs, vals, dots);
   SB_LAUNCH_CHECK();
+  const bool long_walk = max_q_len >= 64;
+  if (long_walk && d >= 16 && d <= 128 && (d & 3) == 0) {
+    int rg = 4;
+    while (rg * 4 < d) rg <<= 1;
+    const int chunk = 16, warps = d <= 64 ? 2 : 4, cols = warps * (32 / rg) * 4;
+    const dim3 grid(H, num_seqs, (d + cols - 1) / cols);
+    const size_t smem = (size_t)2 * chunk * (5 * rg * 4 + cols + 4) * sizeof(float);
+#define SB_GD_PATCH(RG_)                                                                                        \
+  do {                                                                                                          \
+    if (smem > 48 * 1024)                                                                                       \
+      cudaFuncSetAttribute(general_delta_patch_kernel<RG_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    sb_launch_plain(general_delta_patch_kernel<RG_>, grid, warps * 32, smem, stream, vecs, vals, dots, state, cu_q, \
+                    slots, num_slots, H, d, chunk, out, err);                                                   \
+  } while (0)
+    switch (rg) {
+      case 4: SB_GD_PATCH(4); break;
+      case 8: SB_GD_PATCH(8); break;
+      case 16: SB_GD_PATCH(16); break;
+      default: SB_GD_PATCH(32); break;
+    }
+#undef SB_GD_PATCH
+    SB_LAUNCH_CHECK();
+    return 0;
+  }
   const int rows = d <= 256 ? 8 : 32;
   int rs = 1;
   while (rs * rows < d) rs <<= 1;
-  const bool long_walk = max_q_len >= 64;
   const int threads = long_walk ? 128 : 64;
   int chunk = 1;
   while (chunk < 16 && chunk < max_q_len) chunk <<= 1;
