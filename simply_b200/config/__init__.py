@@ -9,6 +9,7 @@ from typing import Any
 from simply_b200.config.engine_config import EngineConfig
 from simply_b200.config.gemma2 import ConfigError, Gemma2Config
 from simply_b200.config.generax import GeneraxConfig
+from simply_b200.config.nulezen import NulezenConfig
 from simply_b200.config.sapivik import SapivikConfig
 from simply_b200.config.zesapel import ZesapelConfig
 from simply_b200.config.model_spec import LayerCall, LayerSpec, ModelSpec, PartSpec
@@ -62,6 +63,6 @@ def preset(name: str):
 
 __all__ = [
     "ConfigError", "EngineConfig", "Gemma2Config", "GeneraxConfig", "LayerCall", "LayerSpec", "ModelSpec",
-    "PartSpec", "SapivikConfig", "ZesapelConfig", "config_from_dict", "load_config", "preset", "preset_dict", "preset_names",
+    "NulezenConfig", "PartSpec", "SapivikConfig", "ZesapelConfig", "config_from_dict", "load_config", "preset", "preset_dict", "preset_names",
     "read_config_json",
 ]

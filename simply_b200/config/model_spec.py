@@ -49,12 +49,15 @@ class LayerCall:
   writes_cache: False for a call that only reads a cache another call wrote.
   add_embedding: True adds the embedding's output (the stream as it stood before the first
     layer) to the stream once more, right before this call.
+  stream_input: (name of one of the model's `stream_inputs`, pass number): that step rewrites the
+    stream right before this call (it sees the embedding's output as well).
   """
 
   layer: str
   cache: str | None = None
   writes_cache: bool = True
   add_embedding: bool = False
+  stream_input: tuple[str, int] | None = None
 
 
 @dataclasses.dataclass(frozen=True)
@@ -68,6 +71,8 @@ class ModelSpec:
   run_order: tuple[LayerCall, ...]
   final_norm: PartSpec
   head: PartSpec
+  # Steps that rewrite the stream between layer calls, by name (registry STREAM_INPUTS).
+  stream_inputs: Mapping[str, PartSpec] = dataclasses.field(default_factory=dict)
 
   def layer(self, name: str) -> LayerSpec:
     for l in self.layers:
@@ -88,6 +93,9 @@ class ModelSpec:
     written: set[str] = set()
     for call, cache in zip(self.run_order, self.cache_names()):
       self.layer(call.layer)
+      if call.stream_input is not None and call.stream_input[0] not in self.stream_inputs:
+        raise ValueError(f"layer call {call.layer!r} names the stream input {call.stream_input[0]!r}, "
+                         "which the model does not define")
       if call.writes_cache:
         written.add(cache)
       elif cache not in written:

@@ -15,6 +15,8 @@ and a layer without a feed-forward has only the first line.
 `pre_norm` is the same without post norms (use_post_ln=False).
 `parallel_residual` has one norm whose output both sublayers read:
   h += mixer(norm(h)) + feed_forward(norm(h))
+With `branch_scales` each result is first multiplied by a learned factor per channel:
+  h += s_mixer * mixer(norm(h)) + s_ff * feed_forward(norm(h))
 """
 
 from __future__ import annotations
@@ -26,7 +28,7 @@ import torch
 from simply_b200.config.model_spec import PartSpec
 from simply_b200.parts.base import Block, FeedForward, Mixer, Norm, build_part
 from simply_b200.parts.feedforward import NoFeedForward
-from simply_b200.parts.norm import RMSNorm
+from simply_b200.parts.norm import ChannelScale, DynamicTanh, RMSNorm
 from simply_b200.registry import BLOCKS, NORMS
 from simply_b200.weights.loader import TensorSpec
 
@@ -40,6 +42,7 @@ class ResidualStream:
     self._branch: torch.Tensor | None = None
     self._post: Norm | None = None
     self._second: torch.Tensor | None = None
+    self._second_post: Norm | None = None
     # A stream that is kept several times (`hyper_connection` blocks): float32 [T, copies, width]
     # in place of `h`, and the write that is still to be done (branch, mix [from, to], out [to]).
     self.lanes: torch.Tensor | None = None
@@ -79,8 +82,9 @@ class ResidualStream:
     return self.h.clone() if self.lanes is None else self.lanes.sum(dim=1)
 
   def add(self, branch: torch.Tensor, post_norm: Norm | None, ctx: Any) -> None:
-    if self._branch is not None and self._second is None and post_norm is None:
-      self._second = branch  # rides along: h + first + second in one kernel
+    if self._branch is not None and self._second is None and (
+        post_norm is None or (isinstance(post_norm, ChannelScale) and isinstance(self._post, (ChannelScale, type(None))))):
+      self._second, self._second_post = branch, post_norm  # rides along: h + first + second in one kernel
       return
     self.flush(ctx)
     self._branch, self._post = branch, post_norm
@@ -115,9 +119,17 @@ class ResidualStream:
 
   def _combine(self, pre: Norm | None, ctx: Any, rows: torch.Tensor | None):
     ops = ctx.ops
-    branch, post, second = self._branch, self._post, self._second
-    fusable = (post is None or isinstance(post, RMSNorm)) and (pre is None or isinstance(pre, RMSNorm))
-    if fusable and second is None:
+    branch, post, second, second_post = self._branch, self._post, self._second, self._second_post
+    fusable = ((post is None or isinstance(post, RMSNorm)) and (pre is None or isinstance(pre, RMSNorm))
+               and second_post is None)
+    scaled = (isinstance(post, (ChannelScale, type(None))) and isinstance(second_post, (ChannelScale, type(None)))
+              and isinstance(pre, (DynamicTanh, type(None)))
+              and (isinstance(pre, DynamicTanh) or post is not None or second_post is not None))
+    if scaled:
+      # Branches times a factor per channel, then tanh(alpha h) w + b for the reader: one kernel.
+      out = ops.scaled_residual_tanh(self.h, branch, post.weight if post is not None else None, second,
+                                     second_post.weight if second_post is not None else None, pre, rows)
+    elif fusable and second is None:
       out = ops.residual_norm(self.h, branch, post, pre, rows)
     elif fusable:
       out = ops.residual_norm(self.h, branch, post, pre, rows, branch2=second)
@@ -132,10 +144,10 @@ class ResidualStream:
       if branch is not None:
         ops.add_to_residual(h, post.apply(branch, ctx) if post is not None else branch)
       if second is not None:
-        ops.add_to_residual(h, second)
+        ops.add_to_residual(h, second_post.apply(second, ctx) if second_post is not None else second)
       out = pre.apply(h, ctx) if pre is not None else None
     if rows is None:
-      self._branch = self._post = self._second = None
+      self._branch = self._post = self._second = self._second_post = None
     return out
 
 
@@ -217,7 +229,9 @@ class ParallelResidualBlock(Block):
   results are added to the stream."""
 
   def __init__(self, prefix: str, width: int, norm: PartSpec, mixer: Mixer, feed_forward: FeedForward,
-               names: dict[str, str] | None = None):
+               names: dict[str, str] | None = None, branch_scales: dict[str, str] | None = None):
+    """`branch_scales`: {"mixer": name, "feed_forward": name}, tensors [width] after the layer's
+    prefix by which the sublayers' results are multiplied before they join the stream."""
     self.prefix = prefix
     self.mixer = mixer
     self.feed_forward = None if isinstance(feed_forward, NoFeedForward) else feed_forward
@@ -226,9 +240,17 @@ class ParallelResidualBlock(Block):
     if role is not None:
       params["name"] = f"{prefix}.{role}"  # the scale's whole tensor name
     self.norm = build_part(NORMS, PartSpec(norm.kind, f"{prefix}.norm", params))
+    scales = branch_scales or {}
+    def scale(role: str):
+      if role not in scales:
+        return None
+      return ChannelScale(f"{prefix}.{scales[role]}", width, name=f"{prefix}.{scales[role]}")
+    self.mixer_scale = scale("mixer")
+    self.feed_forward_scale = scale("feed_forward") if self.feed_forward is not None else None
 
   def _parts(self) -> list:
-    return [p for p in (self.mixer, self.feed_forward, self.norm) if p is not None]
+    return [p for p in (self.mixer, self.feed_forward, self.norm, self.mixer_scale, self.feed_forward_scale)
+            if p is not None]
 
   def cache_need(self):
     return self.mixer.cache_need()
@@ -246,6 +268,6 @@ class ParallelResidualBlock(Block):
 
   def forward(self, stream: ResidualStream, ctx: Any, cache: Any, writes_cache: bool = True) -> None:
     y = stream.normed(self.norm, ctx)
-    stream.add(self.mixer.forward(y, ctx, cache, writes_cache), None, ctx)
+    stream.add(self.mixer.forward(y, ctx, cache, writes_cache), self.mixer_scale, ctx)
     if self.feed_forward is not None:
-      stream.add(self.feed_forward.forward(y, ctx), None, ctx)
+      stream.add(self.feed_forward.forward(y, ctx), self.feed_forward_scale, ctx)

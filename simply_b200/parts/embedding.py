@@ -3,7 +3,8 @@
 `token_embedding`: rows of the table times a constant, sqrt(width) for Gemma 2
 (simply/utils/module.py:450-481).  `tied_head`: logits = x . table^T with the
 same table, no bias, then the final soft cap (simply/model_lib.py:3183-3188,
-simply/utils/module.py:416-433); logits are produced in float32.  `linear_head`
+simply/utils/module.py:416-433); logits are produced in float32.  `logit_scale` multiplies them
+(float32, before the cap).  `linear_head`
 is the same with a table of its own.
 """
 
@@ -69,9 +70,10 @@ class TiedHead(Head):
 
   graph_safe = True
 
-  def __init__(self, prefix: str, embedding: Embedding, logit_softcap: float = 0.0):
+  def __init__(self, prefix: str, embedding: Embedding, logit_softcap: float = 0.0, logit_scale: float = 1.0):
     self.embedding = embedding
     self.logit_softcap = float(logit_softcap or 0.0)
+    self.logit_scale = float(logit_scale)
 
   def tensor_specs(self) -> list[TensorSpec]:
     # A folder may repeat the tied table under the output layer's name.
@@ -89,6 +91,8 @@ class TiedHead(Head):
             "the embedding table, so the folder may repeat the table but not hold another one"])
 
   def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
+    if self.logit_scale != 1.0:
+      return ctx.ops.lm_head(x, self.embedding.table, self.logit_softcap, scale=self.logit_scale)
     return ctx.ops.lm_head(x, self.embedding.table, self.logit_softcap)
 
 

@@ -2,7 +2,8 @@
 
 Per token y:
 
-  z = W_r y                                 router logits, float32, one per expert (identity ones too)
+  z = W_r y (+ b_r)                         router logits, float32, one per expert (identity ones too;
+                                            `router_bias`: a learned offset per expert, tensor `router.b`)
   s = softmax(z)   (`score` "sigmoid": sigmoid(z))
   chosen = the `top` experts with the largest s + c   (`correction`: c is a learned number per
            expert that shifts the choice only)
@@ -12,7 +13,10 @@ Per token y:
 expert_e(y) = W_down (act(W_gate y) * (W_up y)) for e < num_experts; the last `num_identity`
 router outputs are identity experts without tensors: expert_e(y) = y.  The shared expert has the
 same form with a hidden size of its own, runs for every token, and is gated by one number per token
-(`shared_gate`; without it it is added as it is).
+(`shared_gate`; without it it is added as it is).  With softmax scores and `renormalize` the
+weights are the softmax over the chosen experts' logits alone.  The activation `clamped_swish`
+acts on both halves (g' = min(g, L), u' = clamp(u, -L, L), g' sigmoid(1.702 g') (u' + 1)) with
+`limit` L for the routed experts and `shared_limit` for the shared one.
 
 The experts' matrices are stacked into [experts, 2 hidden, width] (gate rows, then up rows) and
 [experts, width, hidden]; the tokens of a step are sorted by expert on the device and every expert
@@ -43,7 +47,8 @@ class RoutedExperts(FeedForward):
   def __init__(self, prefix: str, width: int, hidden: int, num_experts: int, top: int, activation: str = "silu",
                num_identity: int = 0, weight_scale: float = 1.0, score: str = "softmax", correction: bool = False,
                renormalize: bool = False, shared_hidden: int = 0, shared_gate: bool = False,
-               names: dict[str, str] | None = None):
+               names: dict[str, str] | None = None, router_bias: bool = False, limit: float = 0.0,
+               shared_limit: float | None = None):
     if score not in _SCORES:
       raise ValueError(f"{prefix}: router score must be one of {sorted(_SCORES)}, got {score!r}")
     if not 1 <= top <= num_experts + num_identity:
@@ -51,8 +56,13 @@ class RoutedExperts(FeedForward):
     self.prefix, self.width, self.hidden = prefix, width, hidden
     self.num_experts, self.num_identity, self.top = num_experts, num_identity, top
     self.activation = ACTIVATIONS.get(activation)
-    if self.activation > 2:
-      raise ValueError(f"{prefix}: experts take the activations gelu_tanh, silu and relu")
+    if self.activation > 3:
+      raise ValueError(f"{prefix}: experts take the activations gelu_tanh, silu, relu and clamped_swish")
+    self.limit = float(limit)
+    self.shared_limit = self.limit if shared_limit is None else float(shared_limit)
+    if self.activation == 3 and not (self.limit > 0 and self.shared_limit > 0):
+      raise ValueError(f"{prefix}: the clamped activation needs positive limits")
+    self.has_router_bias = bool(router_bias)
     self.weight_scale, self.score = float(weight_scale), _SCORES[score]
     self.has_correction, self.renormalize = bool(correction), bool(renormalize)
     self.shared_hidden, self.has_shared_gate = shared_hidden, bool(shared_gate and shared_hidden)
@@ -68,6 +78,8 @@ class RoutedExperts(FeedForward):
                      Linear(f"{sp}.{n['down']}", width, shared_hidden))
     self.router_name = f"{prefix}.{n['router']}"
     self.correction_name = f"{prefix}.{n['correction']}"
+    self.router_bias_name = f"{prefix}.{n['router']}.{n.get('bias', 'b')}"
+    self.router_bias = None
     self.shared_gate_name = f"{prefix}.{n['shared_gate']}"
     self.gate_up = self.down = self.router = self.correction = self.shared_gate_w = None
     self.shared_gate_up = None
@@ -76,6 +88,8 @@ class RoutedExperts(FeedForward):
     total = self.num_experts + self.num_identity
     specs = [p.spec() for trio in self.experts for p in trio]
     specs.append(TensorSpec(self.router_name, (total, self.width), "matrix", precision="stored"))
+    if self.has_router_bias:
+      specs.append(TensorSpec(self.router_bias_name, (total,), "scale", precision="stored"))
     if self.has_correction:
       specs.append(TensorSpec(self.correction_name, (total,), "scale", precision="stored"))
     if self.shared is not None:
@@ -91,6 +105,7 @@ class RoutedExperts(FeedForward):
       self.down = torch.stack([t[d.name] for _, _, d in self.experts]).contiguous()
     self.router = t[self.router_name].float().contiguous()
     self.correction = t[self.correction_name].float().contiguous() if self.has_correction else None
+    self.router_bias = t[self.router_bias_name].float().contiguous() if self.has_router_bias else None
     if self.shared is not None:
       self.shared_gate_up = fuse_rows([t[self.shared[0].name], t[self.shared[1].name]])
       self.shared[2].bind(tensors)
@@ -99,14 +114,20 @@ class RoutedExperts(FeedForward):
 
   def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
     ops = ctx.ops
+    # (only what differs from the plain case is passed on: see HeadNormAttention._store_options)
+    more = {"bias": self.router_bias} if self.router_bias is not None else {}
     chosen, weight, gate = ops.route_tokens(
         x, self.router, self.correction, self.shared_gate_w, top=self.top, scale=self.weight_scale,
-        score=self.score, renormalize=self.renormalize)
+        score=self.score, renormalize=self.renormalize, **more)
     shared = None
     if self.shared is not None:
-      shared = self.shared[2](ops.gated_linear(x, self.shared_gate_up, self.activation), ctx)
+      if self.activation == 3:
+        shared = self.shared[2](ops.gated_linear(x, self.shared_gate_up, self.activation, limit=self.shared_limit), ctx)
+      else:
+        shared = self.shared[2](ops.gated_linear(x, self.shared_gate_up, self.activation), ctx)
+    more = {"limit": self.limit} if self.activation == 3 else {}
     return ops.mix_experts(x, chosen, weight, self.gate_up, self.down, self.num_experts, self.activation,
-                           shared, gate)
+                           shared, gate, **more)
 
 
 @FEED_FORWARDS.register("table_experts")

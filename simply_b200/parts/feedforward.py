@@ -65,6 +65,41 @@ class GatedFeedForward(FeedForward):
     return self.down_proj(z, ctx)
 
 
+@FEED_FORWARDS.register("learned_activation")
+class LearnedActivationFeedForward(FeedForward):
+  """down(act(up(x))) without a gate, no biases, with an activation that has learned numbers.
+
+  `activation` "xielu": two numbers p, q (tensor `act`, [2]) give a_p = softplus(p) and
+  a_n = 1/2 + softplus(q), both in float32;
+    z > 0:   a_p z^2 + z / 2
+    z <= 0:  a_n (e^z - 1 - z) + z / 2
+  """
+
+  graph_safe = True
+
+  def __init__(self, prefix: str, width: int, hidden: int, activation: str = "xielu",
+               names: dict[str, str] | None = None):
+    if activation != "xielu":
+      raise ValueError(f"{prefix}: known learned activations: xielu")
+    names = names or {}
+    self.prefix, self.width, self.hidden = prefix, width, hidden
+    self.up_proj = Linear(f"{prefix}.{names.get('up', 'up')}", hidden, width)
+    self.down_proj = Linear(f"{prefix}.{names.get('down', 'down')}", width, hidden)
+    self.act_name = f"{prefix}.{names.get('act', 'act')}"
+    self.act: torch.Tensor | None = None
+
+  def tensor_specs(self) -> list[TensorSpec]:
+    return [self.up_proj.spec(), self.down_proj.spec(), TensorSpec(self.act_name, (2,), "scale", precision="stored")]
+
+  def bind(self, tensors, ops) -> None:
+    self.up_proj.bind(tensors)
+    self.down_proj.bind(tensors)
+    self.act = tensors[self.act_name].float().contiguous()
+
+  def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
+    return self.down_proj(ctx.ops.linear_xielu(x, self.up_proj.weight, self.act), ctx)
+
+
 @FEED_FORWARDS.register("none")
 class NoFeedForward(FeedForward):
   """A layer without a feed-forward: block arrangements skip it."""

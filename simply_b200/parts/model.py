@@ -17,7 +17,7 @@ import torch
 from simply_b200.config.model_spec import ModelSpec
 from simply_b200.parts.base import Block, build_part
 from simply_b200.parts.block import ResidualStream
-from simply_b200.registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS
+from simply_b200.registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, STREAM_INPUTS
 from simply_b200.weights.loader import TensorSpec
 
 # Importing the part modules registers the built-in parts.
@@ -35,6 +35,7 @@ from simply_b200.parts import embedding as _embedding  # noqa: F401
 from simply_b200.parts import feedforward as _feedforward  # noqa: F401
 from simply_b200.parts import norm as _norm  # noqa: F401
 from simply_b200.parts import position as _position  # noqa: F401
+from simply_b200.parts import stream_input as _stream_input  # noqa: F401
 
 
 class DecoderModel:
@@ -49,6 +50,7 @@ class DecoderModel:
       feed_forward = build_part(FEED_FORWARDS, layer.feed_forward)
       self.blocks[layer.name] = build_part(BLOCKS, layer.block, mixer=mixer,
                                            feed_forward=feed_forward)
+    self.stream_inputs = {name: build_part(STREAM_INPUTS, part) for name, part in spec.stream_inputs.items()}
     self.final_norm = build_part(NORMS, spec.final_norm)
     self.head = build_part(HEADS, spec.head, embedding=self.embedding)
     self.cache_names = spec.cache_names()
@@ -58,6 +60,8 @@ class DecoderModel:
     specs = self.embedding.tensor_specs()
     for block in self.blocks.values():
       specs += block.tensor_specs()
+    for part in self.stream_inputs.values():
+      specs += part.tensor_specs()
     specs += self.final_norm.tensor_specs() + self.head.tensor_specs()
     names = [s.name for s in specs]
     if len(set(names)) != len(names):
@@ -69,13 +73,16 @@ class DecoderModel:
     self.embedding.bind(tensors, ops)
     for block in self.blocks.values():
       block.bind(tensors, ops)
+    for part in self.stream_inputs.values():
+      part.bind(tensors, ops)
     self.final_norm.bind(tensors, ops)
     self.head.bind(tensors, ops)
 
   def graph_safe(self) -> bool:
     """True if every part allows a decode step to be captured in a CUDA graph."""
     return (self.embedding.graph_safe and self.head.graph_safe and self.final_norm.graph_safe
-            and all(b.graph_safe for b in self.blocks.values()))
+            and all(b.graph_safe for b in self.blocks.values())
+            and all(p.graph_safe for p in self.stream_inputs.values()))
 
   # ---- caches ---------------------------------------------------------------
   def cache_needs(self) -> dict[str, Any]:
@@ -114,11 +121,16 @@ class DecoderModel:
       again = ctx.ops.cast(first, ctx.ops.dtype) if exact else first
       if again is first:
         again = first.clone()
+    if self.stream_inputs:
+      first, kept = first.clone(), first  # the stream is updated in place: the steps read a copy
     stream = ResidualStream(first)
     layer_outputs = ctx.memo.get("layer_outputs")  # a list: the stream after every layer call (debugging, tests)
     for call, cache in zip(self.spec.run_order, self.cache_names):
       if call.add_embedding:
         stream.add_input(again, ctx)
+      if call.stream_input is not None:
+        name, index = call.stream_input
+        self.stream_inputs[name].forward(stream, kept, index, ctx)
       self.blocks[call.layer].forward(stream, ctx, caches.get(cache), call.writes_cache)
       if layer_outputs is not None:
         layer_outputs.append(stream.total(ctx))

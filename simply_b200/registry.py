@@ -1,7 +1,8 @@
 """Name -> class/function registries.
 
 Every pluggable thing in the engine (architectures, embeddings, output layers, mixers,
-feed-forwards, norms, position encodings, block arrangements, activations) lives in one of
+feed-forwards, norms, position encodings, block arrangements, steps on the stream between
+layers, activations) lives in one of
 these registries under a string name.  A model description refers to parts by
 name only, so a new part is added by registering it; no framework file has to
 change.
@@ -69,4 +70,5 @@ FEED_FORWARDS: Registry[Any] = Registry("feed_forward")
 NORMS: Registry[Any] = Registry("norm")
 POSITION_ENCODINGS: Registry[Any] = Registry("position_encoding")
 BLOCKS: Registry[Any] = Registry("block")
+STREAM_INPUTS: Registry[Any] = Registry("stream_input")
 ACTIVATIONS: Registry[int] = Registry("activation")

@@ -52,8 +52,8 @@ class ReferenceOps:
       out = out + position_table[positions.long()].float()
     return out
 
-  def lm_head(self, x, table, cap):
-    logits = x.float() @ table.float().t()
+  def lm_head(self, x, table, cap, scale=1.0):
+    logits = (x.float() @ table.float().t()) * scale
     if cap > 0:
       logits = cap * torch.tanh(logits / cap)
     return logits
@@ -98,6 +98,44 @@ class ReferenceOps:
     if pre is None:
       return None
     return self._rms(h, pre.weight, pre.eps, pre.plus_one).to(self.dtype)
+
+  def scaled_residual_tanh(self, h, branch, scale, branch2, scale2, pre, rows):
+    """h += scale * branch + scale2 * branch2 (float32, in place unless `rows` picks some);
+    returns tanh(alpha h) w + b for the norm `pre`, or None without one."""
+    if rows is not None:
+      idx = rows.long()
+      h = h[idx].float().clone()
+      branch = branch[idx] if branch is not None else None
+      branch2 = branch2[idx] if branch2 is not None else None
+    elif h.dtype != torch.float32:
+      h = h.float()
+    add = None
+    for b, s in ((branch, scale), (branch2, scale2)):
+      if b is not None:
+        term = b.float() * (s.float() if s is not None else 1.0)
+        add = term if add is None else add + term
+    if add is not None:
+      h += add
+    if pre is None:
+      return None
+    return (torch.tanh(pre.alpha.float() * h) * pre.weight.float() + pre.bias.float()).to(self.dtype)
+
+  def scale_channels(self, x, w):
+    return (x.float() * w.float()).to(self.dtype)
+
+  def pack_pair(self, a, b):
+    return torch.cat([a, b], dim=1).to(self.dtype)
+
+  def linear_wide(self, x, w, row=None):
+    out = x.float() @ w.float().t()
+    return out + row.float() if row is not None else out
+
+  def linear_xielu(self, x, w, act):
+    z = self.linear(x, w).float()
+    ap = torch.nn.functional.softplus(act[0].float())
+    an = 0.5 + torch.nn.functional.softplus(act[1].float())
+    zn = torch.clamp(z, max=0.0)
+    return torch.where(z > 0, ap * z * z + 0.5 * z, an * (torch.expm1(zn) - zn) + 0.5 * z).to(self.dtype)
 
   def gather_rows(self, x, rows):
     return x[rows.long()].clone()
@@ -144,11 +182,13 @@ class ReferenceOps:
 
   # ---- attention ------------------------------------------------------------
   def paged_attention(self, q, storage, block_table, ctx, *, num_heads, num_kv_heads, head_dim,
-                      logit_softcap, window, value_dim=None, pooled=None, values_in_keys=False, sink=None):
-    if pooled is not None or (value_dim is not None and value_dim != head_dim) or values_in_keys or sink is not None:
+                      logit_softcap, window, value_dim=None, pooled=None, values_in_keys=False, sink=None,
+                      distance_bias=None):
+    if (pooled is not None or (value_dim is not None and value_dim != head_dim) or values_in_keys or sink is not None
+        or distance_bias is not None):
       assert not logit_softcap
       return self._general_attention(q, storage, block_table, ctx, num_heads, num_kv_heads, head_dim,
-                                     value_dim or head_dim, window, pooled, values_in_keys, sink)
+                                     value_dim or head_dim, window, pooled, values_in_keys, sink, distance_bias)
     t = q.shape[0]
     out = torch.zeros(t, num_heads, head_dim, dtype=torch.float32, device=q.device)
     group = num_heads // num_kv_heads
@@ -247,7 +287,7 @@ class ReferenceOps:
     return y.reshape(t, num_heads * dim).to(self.dtype)
 
   def _general_attention(self, q, storage, block_table, ctx, num_heads, num_kv_heads, head_dim, value_dim,
-                         window, pooled, values_in_keys=False, sink=None):
+                         window, pooled, values_in_keys=False, sink=None, distance_bias=None):
     t = q.shape[0]
     ps = ctx.page_size
     if values_in_keys:  # one row per entry: the key, whose first value_dim numbers are the value
@@ -283,6 +323,9 @@ class ReferenceOps:
         for n in range(num_heads):
           m = n // group
           scores = k[:, m] @ q[r, n].float()
+          if distance_bias is not None:  # [2, heads]: the score loses r1 log(1 + r2 distance)
+            assert pooled is None
+            scores = scores - distance_bias[0, n] * torch.log1p(distance_bias[1, n] * (i - j).float())
           if sink is None:
             p = torch.softmax(scores, dim=0)
           else:  # the denominator also holds exp(sink[n]), which has no value
@@ -294,12 +337,16 @@ class ReferenceOps:
 
   # ---- attention with heads normed one by one -----------------------------------
   def rotate_headnorm_store(self, proj, eps, q_scale, rot_freq, *, interleaved, head_norm, tie_values, num_heads,
-                            num_kv_heads, head_dim, storage, block_table, ctx):
+                            num_kv_heads, head_dim, storage, block_table, ctx, value_dim=None, bias=None):
     t = proj.shape[0]
-    nq, nk = num_heads * head_dim, num_kv_heads * head_dim
-    q = proj[:, :nq].float().reshape(t, num_heads, head_dim)
-    k_raw = proj[:, nq:nq + nk].float().reshape(t, num_kv_heads, head_dim)
-    v = k_raw if tie_values else proj[:, nq + nk:nq + 2 * nk].float().reshape(t, num_kv_heads, head_dim)
+    value_dim = head_dim if value_dim is None else value_dim
+    nq, nk, nv = num_heads * head_dim, num_kv_heads * head_dim, (0 if tie_values else num_kv_heads * value_dim)
+    cols = proj[:, :nq + nk + nv].float()
+    if bias is not None:  # on q, k and v, before anything else
+      cols = cols + bias.float()
+    q = cols[:, :nq].reshape(t, num_heads, head_dim)
+    k_raw = cols[:, nq:nq + nk].reshape(t, num_kv_heads, head_dim)
+    v = k_raw if tie_values else cols[:, nq + nk:].reshape(t, num_kv_heads, value_dim)
 
     def prepare(x):
       x = x.clone()
@@ -320,8 +367,9 @@ class ReferenceOps:
       pos = ctx.positions.long()
       page = block_table[ctx.token_seq.long(), pos // ps].long()
       assert (page >= 0).all(), "a token would be written to a page the request does not hold"
-      storage[page, 0, :, pos % ps, :] = prepare(k_raw).to(storage.dtype)
-      storage[page, 1, :, pos % ps, :] = v.to(storage.dtype)
+      keys, values = self._kv_views(storage, num_kv_heads, ps, head_dim, value_dim)
+      keys[page, :, pos % ps, :] = prepare(k_raw).to(storage.dtype)
+      values[page, :, pos % ps, :] = v.to(storage.dtype)
     return (prepare(q) * q_scale).to(self.dtype)
 
   def sigmoid_gate(self, x, proj, offset, per=1):
@@ -348,8 +396,10 @@ class ReferenceOps:
     return out
 
   # ---- routed experts ---------------------------------------------------------------
-  def route_tokens(self, x, router, correction, shared_gate_w, *, top, scale, score=0, renormalize=False):
+  def route_tokens(self, x, router, correction, shared_gate_w, *, top, scale, score=0, renormalize=False, bias=None):
     z = x.float() @ router.float().t()
+    if bias is not None:
+      z = z + bias.float()
     s = torch.softmax(z, dim=-1) if score == 0 else torch.sigmoid(z)
     choice = s + (correction.float() if correction is not None else 0.0)
     chosen = torch.argsort(-choice, dim=-1, stable=True)[:, :top]
@@ -370,7 +420,8 @@ class ReferenceOps:
     chosen = table[token_ids.long()].to(torch.int32)
     return chosen, torch.full(chosen.shape, 1.0 / chosen.shape[1], dtype=torch.float32, device=chosen.device)
 
-  def mix_experts(self, x, chosen, weight, gate_up, down, num_experts, activation, shared, shared_gate, gated=True):
+  def mix_experts(self, x, chosen, weight, gate_up, down, num_experts, activation, shared, shared_gate, gated=True,
+                  limit=0.0):
     xf = x.float()
     out = torch.zeros_like(xf)
     for t in range(x.shape[0]):
@@ -380,7 +431,7 @@ class ReferenceOps:
           h = self._activation(xf[t:t + 1] @ gate_up[e].float().t(), activation).to(self.dtype)
           y = (h.float() @ down[e].float().t()).to(self.dtype).float()[0]
         elif e < num_experts:
-          h = self.gated_activation((xf[t:t + 1] @ gate_up[e].float().t()).to(self.dtype), activation)
+          h = self.gated_activation((xf[t:t + 1] @ gate_up[e].float().t()).to(self.dtype), activation, limit)
           y = (h.float() @ down[e].float().t()).to(self.dtype).float()[0]
         else:
           y = xf[t]
