@@ -19,7 +19,8 @@
 // are visited in tiles of 32 by block number, before the tokens.  `tied`: an entry has one row of
 // head_dim numbers whose first v_dim are its value as well (a cache of latents; a page then holds
 // key rows only).  `sink`: one learned number per query head whose exponential joins the softmax's
-// denominator; it has no key and no value.
+// denominator; it has no key and no value.  `distance`: two learned numbers r1, r2 per query head
+// ([2, heads]); the score of query i and key j loses r1 * log(1 + r2 * (i - j)) (float32, log1pf).
 //
 // This is the true 32-bit path's attention and the fallback of the bfloat16
 // path for shapes its tensor-core kernels refuse.
@@ -55,7 +56,7 @@ template <> struct Vec16<bf16> {
 // `kr` / `vr` are this lane's key and value rows (null where the lane has no key).
 template <typename KT>
 __device__ __forceinline__ void gen_tile(const KT* kr, const KT* vr, const float* qs, int head_dim, int v_dim,
-                                         float cap, int lane, float& m_run, float& l_run, float* acc) {
+                                         float cap, float minus, int lane, float& m_run, float& l_run, float* acc) {
   constexpr int VN = Vec16<KT>::N;
   const float NEG = -0.5f * FLT_MAX;  // the reference's mask value, simply/utils/common.py:543-551
   const bool valid = kr != nullptr;
@@ -73,7 +74,7 @@ __device__ __forceinline__ void gen_tile(const KT* kr, const KT* vr, const float
     } else {
       for (; d < head_dim; ++d) dot = fmaf(qs[d], to_f32<KT>(kr[d]), dot);
     }
-    s = cap > 0.f ? cap * tanhf(dot / cap) : dot;
+    s = (cap > 0.f ? cap * tanhf(dot / cap) : dot) - minus;
   }
   const float m_new = fmaxf(m_run, warp_max(s));
   const float alpha = expf(m_run - m_new);
@@ -120,7 +121,9 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
                                int head_dim, int v_dim, int page_size, int num_pages, float cap, int window,
                                const T* __restrict__ pool, const int* __restrict__ pool_table,
                                int pool_max_pages, int pool_len, int pool_pages, int tied,
-                               const float* __restrict__ sink, int* err) {
+                               const float* __restrict__ sink, const float* __restrict__ distance, int* err) {
+  const float r1 = distance != nullptr ? distance[blockIdx.x % num_q_heads] : 0.f;  // (weights: before the wait)
+  const float r2 = distance != nullptr ? distance[num_q_heads + blockIdx.x % num_q_heads] : 0.f;
   pdl_wait_block();
   pdl_launch_dependents();
   // head_dim floats of q, then per warp its running maximum, sum and v_dim partial results
@@ -162,7 +165,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
           vr = pool + page * page_stride + (size_t)num_kv_heads * entries * head_dim + row * v_dim;
         }
       }
-      gen_tile<T>(kr, vr, qs, head_dim, v_dim, cap, lane, m_run, l_run, acc);
+      gen_tile<T>(kr, vr, qs, head_dim, v_dim, cap, 0.f, lane, m_run, l_run, acc);
     }
   }
 
@@ -183,7 +186,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
         vr = tied ? kr : cache + page * page_stride + value_base + row * v_dim;
       }
     }
-    gen_tile<T>(kr, vr, qs, head_dim, v_dim, cap, lane, m_run, l_run, acc);
+    const float minus = distance != nullptr && j <= pos ? r1 * log1pf(r2 * (float)(pos - j)) : 0.f;
+    gen_tile<T>(kr, vr, qs, head_dim, v_dim, cap, minus, lane, m_run, l_run, acc);
   }
   // The warps' parts meet in warp order (the same order whatever the step holds).
   float* mine = part + (size_t)warp * (v_dim + 2);
@@ -225,8 +229,10 @@ extern "C" int sb_paged_attention_general(const void* q, int dtype, const void* 
                                           int head_dim, int v_dim, int page_size, int num_pages, float cap,
                                           int window, const void* pool, const int* pool_table,
                                           int pool_max_pages, int pool_len, int pool_pages, int tied,
-                                          const float* sink, int* err, cudaStream_t stream) {
+                                          const float* sink, const float* distance, int* err,
+                                          cudaStream_t stream) {
   if (num_tokens == 0) return 0;
+  if (distance != nullptr && pool != nullptr) return -13;
   if (tied && (pool != nullptr || v_dim > head_dim)) return -13;
   // (the values' sums live in registers, GEN_MAX_DPL per lane; a key row only passes through)
   if (head_dim <= 0 || head_dim > 4096 || v_dim <= 0 || v_dim > 32 * GEN_MAX_DPL) return -7;
@@ -239,12 +245,12 @@ extern "C" int sb_paged_attention_general(const void* q, int dtype, const void* 
     sb_launch(paged_attention_generic_kernel<float>, blocks, GEN_WARPS * 32, smem, stream, (const float*)q,
         (const float*)cache, block_table, max_pages, token_seq, positions, (float*)out, num_tokens,
         num_q_heads, num_kv_heads, head_dim, v_dim, page_size, num_pages, cap, window, (const float*)pool, pool_table,
-        pool_max_pages, pool_len, pool_pages, tied, sink, err);
+        pool_max_pages, pool_len, pool_pages, tied, sink, distance, err);
   else
     sb_launch(paged_attention_generic_kernel<bf16>, blocks, GEN_WARPS * 32, smem, stream, (const bf16*)q,
         (const bf16*)cache, block_table, max_pages, token_seq, positions, (bf16*)out, num_tokens,
         num_q_heads, num_kv_heads, head_dim, v_dim, page_size, num_pages, cap, window, (const bf16*)pool, pool_table,
-        pool_max_pages, pool_len, pool_pages, tied, sink, err);
+        pool_max_pages, pool_len, pool_pages, tied, sink, distance, err);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -256,5 +262,5 @@ extern "C" int sb_paged_attention_generic(const void* q, int dtype, const void* 
                                           int* err, cudaStream_t stream) {
   return sb_paged_attention_general(q, dtype, cache, block_table, max_pages, token_seq, positions, out, num_tokens,
                                     num_q_heads, num_kv_heads, head_dim, head_dim, page_size, num_pages, cap,
-                                    window, nullptr, nullptr, 0, 0, 0, 0, nullptr, err, stream);
+                                    window, nullptr, nullptr, 0, 0, 0, 0, nullptr, nullptr, err, stream);
 }

@@ -359,7 +359,7 @@ extern "C" int sb_rotate_heads(const void* x, int dtype, const int* positions, c
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
-rotate_headnorm_store_kernel(const T* __restrict__ proj, int row_width, float eps, float q_scale,
+rotate_headnorm_store_kernel(const T* __restrict__ proj, int row_width, const float* __restrict__ bias, float eps, float q_scale,
                              const float* __restrict__ rot_freq, int rot_dims, int interleaved, int head_norm,
                              int tie_values, T* __restrict__ q_out, T* __restrict__ cache,
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ token_seq,
@@ -374,7 +374,8 @@ rotate_headnorm_store_kernel(const T* __restrict__ proj, int row_width, float ep
   const T* x = proj + (size_t)t * row_width;
   const float pos = (float)positions[t];
   for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * rot_freq[i], cs + half + i, cs + i);
-  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) row[i] = to_f32<T>(x[i]);
+  // `bias`: a learned offset on q, k and (untied) v, added in float32 before anything else
+  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) row[i] = to_f32<T>(x[i]) + (bias != nullptr ? bias[i] : 0.f);
   __syncthreads();
 
   long long page = -1;
@@ -428,12 +429,13 @@ rotate_headnorm_store_kernel(const T* __restrict__ proj, int row_width, float ep
     T* dst = cache + page * page_stride + (size_t)G * page_size * d;
     for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
       const int m = i / dv, c = i - m * dv;
-      dst[((size_t)m * page_size + off) * dv + c] = vx[i];
+      dst[((size_t)m * page_size + off) * dv + c] =
+          bias != nullptr ? from_f32<T>(to_f32<T>(vx[i]) + bias[nq + nk + i]) : vx[i];
     }
   }
 }
 
-extern "C" int sb_rotate_headnorm_store(const void* proj, int row_width, int dtype, float eps, float q_scale,
+extern "C" int sb_rotate_headnorm_store(const void* proj, int row_width, int dtype, const float* bias, float eps, float q_scale,
                                         const float* rot_freq, int rot_dims, int interleaved, int head_norm,
                                         int tie_values, void* q_out, void* cache, const int* block_table,
                                         int max_pages, const int* token_seq, const int* positions, int num_tokens,
@@ -446,12 +448,12 @@ extern "C" int sb_rotate_headnorm_store(const void* proj, int row_width, int dty
   if (rot_dims % 2 || rot_dims > d || (tie_values && dv != d)) return -4;
   if (dtype == SB_DTYPE_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(rotate_headnorm_store_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb_launch(rotate_headnorm_store_kernel<float>, num_tokens, 256, smem, stream, (const float*)proj, row_width, eps,
+    sb_launch(rotate_headnorm_store_kernel<float>, num_tokens, 256, smem, stream, (const float*)proj, row_width, bias, eps,
               q_scale, rot_freq, rot_dims, interleaved, head_norm, tie_values, (float*)q_out, (float*)cache,
               block_table, max_pages, token_seq, positions, H, G, d, dv, page_size, num_pages, write_cache, err);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(rotate_headnorm_store_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb_launch(rotate_headnorm_store_kernel<bf16>, num_tokens, 256, smem, stream, (const bf16*)proj, row_width, eps,
+    sb_launch(rotate_headnorm_store_kernel<bf16>, num_tokens, 256, smem, stream, (const bf16*)proj, row_width, bias, eps,
               q_scale, rot_freq, rot_dims, interleaved, head_norm, tie_values, (bf16*)q_out, (bf16*)cache,
               block_table, max_pages, token_seq, positions, H, G, d, dv, page_size, num_pages, write_cache, err);
   }

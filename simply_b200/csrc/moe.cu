@@ -1,7 +1,8 @@
 // Feed-forward layers made of routed experts.  Five kernels, none of which needs the host to
 // know how the tokens were dealt out, so a step can be captured in a CUDA graph:
 //
-//   route    per token: router logits z = W_r x (float32), scores s = softmax(z) (or sigmoid),
+//   route    per token: router logits z = W_r x (+ a learned offset per expert) (float32), scores
+//            s = softmax(z) (or sigmoid),
 //            the `top` experts with the largest s + correction, weights s * scale (optionally
 //            divided by their sum), and the shared expert's gate sigmoid(w_sg . x)
 //   group    the (token, choice) pairs sorted by expert, cut into tiles of TILE_M rows of one
@@ -26,7 +27,8 @@
 template <typename T>
 __global__ void __launch_bounds__(1024)
 moe_route_kernel(const T* __restrict__ x, int width, const float* __restrict__ router_w,
-                 const float* __restrict__ correction, const float* __restrict__ shared_gate_w, int NE, int top,
+                 const float* __restrict__ correction, const float* __restrict__ shared_gate_w,
+                 const float* __restrict__ bias, int NE, int top,
                  float scale, int score_fn, int renormalize, int* __restrict__ chosen, float* __restrict__ weight,
                  float* __restrict__ shared_gate) {
   pdl_wait_block();
@@ -60,7 +62,7 @@ moe_route_kernel(const T* __restrict__ x, int width, const float* __restrict__ r
       for (int c = lane; c < width; c += 32) acc = fmaf(w[c], xs[c], acc);
     }
     acc = warp_sum(acc);
-    if (lane == 0) z[e] = acc;
+    if (lane == 0) z[e] = acc + (bias != nullptr && e < NE ? bias[e] : 0.f);
   }
   __syncthreads();
   if (warp != 0) return;
@@ -107,9 +109,9 @@ moe_route_kernel(const T* __restrict__ x, int width, const float* __restrict__ r
 }
 
 extern "C" int sb_moe_route(const void* x, int dtype, int num_tokens, int width, const float* router_w,
-                            const float* correction, const float* shared_gate_w, int NE, int top, float scale,
-                            int score_fn, int renormalize, int* chosen, float* weight, float* shared_gate,
-                            cudaStream_t stream) {
+                            const float* correction, const float* shared_gate_w, const float* bias, int NE, int top,
+                            float scale, int score_fn, int renormalize, int* chosen, float* weight,
+                            float* shared_gate, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   const size_t smem = ((size_t)width + 2 * NE + 1) * sizeof(float);
   if (top < 1 || top > NE || smem > 200 * 1024) return -13;
@@ -120,11 +122,11 @@ extern "C" int sb_moe_route(const void* x, int dtype, int num_tokens, int width,
   if (dtype == SB_DTYPE_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     sb_launch(moe_route_kernel<float>, num_tokens, 32 * warps, smem, stream, (const float*)x, width, router_w, correction,
-              shared_gate_w, NE, top, scale, score_fn, renormalize, chosen, weight, shared_gate);
+              shared_gate_w, bias, NE, top, scale, score_fn, renormalize, chosen, weight, shared_gate);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     sb_launch(moe_route_kernel<bf16>, num_tokens, 32 * warps, smem, stream, (const bf16*)x, width, router_w, correction,
-              shared_gate_w, NE, top, scale, score_fn, renormalize, chosen, weight, shared_gate);
+              shared_gate_w, bias, NE, top, scale, score_fn, renormalize, chosen, weight, shared_gate);
   }
   SB_LAUNCH_CHECK();
   return 0;
@@ -211,6 +213,17 @@ __device__ __forceinline__ float moe_activation(float g, int act) {
   return fmaxf(g, 0.f);
 }
 
+// act(gate) * up; activation 3 is the clamped form, which acts on both halves:
+// g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1).
+__device__ __forceinline__ float moe_gated_pair(float g, float u, int act, float limit) {
+  if (act == 3) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+  }
+  return moe_activation(g, act) * u;
+}
+
 // 16 bytes from global memory (16-byte aligned) into a tile row (bfloat16 rows are, float rows are not).
 __device__ __forceinline__ void moe_copy16(bf16* dst, const bf16* src) {
   *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
@@ -246,7 +259,7 @@ __global__ void __launch_bounds__(256)
 moe_product_kernel(const T* __restrict__ A, const int* __restrict__ row_pair, int pair_div,
                    const T* __restrict__ W, size_t expert_stride, int second, int K, int N,
                    const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
-                   const int* __restrict__ tile_rows, int act, T* __restrict__ out) {
+                   const int* __restrict__ tile_rows, int act, float limit, T* __restrict__ out) {
   pdl_wait_block();
   pdl_launch_dependents();
   constexpr int BK = MoeTile<T>::K, LD = MoeTile<T>::LD, NST = MoeStages<T>::N;
@@ -414,7 +427,7 @@ moe_product_kernel(const T* __restrict__ A, const int* __restrict__ row_pair, in
       const int r = idx / MOE_TILE_N, c = idx - r * MOE_TILE_N;
       if (n0 + c < N)
         out[(size_t)(row0 + r) * N + n0 + c] =
-            from_f32<T>(moe_activation(Cs[r * CLD + c], act) * Cs[(MOE_TILE_M + r) * CLD + c]);
+            from_f32<T>(moe_gated_pair(Cs[r * CLD + c], Cs[(MOE_TILE_M + r) * CLD + c], act, limit));
     }
   } else {
     for (int idx = threadIdx.x; idx < rows * 2 * MOE_TILE_N; idx += blockDim.x) {
@@ -430,12 +443,12 @@ moe_product_kernel(const T* __restrict__ A, const int* __restrict__ row_pair, in
 
 // gated = 1: W [E, 2 N, K] (gate rows, then up rows), out [P, N] = act(gate) * up;
 // gated = 0: W [E, N, K], out [P, N] = act(sums), act -1: the sums themselves.
-// act: 0 gelu (tanh form), 1 silu, 2 relu, 4 the exact gelu.
+// act: 0 gelu (tanh form), 1 silu, 2 relu, 3 the clamped form with `limit` (gated only), 4 the exact gelu.
 extern "C" int sb_moe_product(const void* A, const int* row_pair, int pair_div, const void* W, int dtype, int gated,
                               int K, int N, const int* tile_expert, const int* tile_row0, const int* tile_rows,
-                              int max_tiles, int act, void* out, cudaStream_t stream) {
+                              int max_tiles, int act, float limit, void* out, cudaStream_t stream) {
   if (max_tiles == 0 || N == 0) return 0;
-  if (K <= 0 || act < (gated ? 0 : -1) || act > 4 || act == 3 || pair_div < 1) return -13;
+  if (K <= 0 || act < (gated ? 0 : -1) || act > 4 || (act == 3 && !(gated && limit > 0.f)) || pair_div < 1) return -13;
   const size_t stride = (size_t)(gated ? 2 : 1) * N * K;
   const int per_block = gated ? MOE_TILE_N : 2 * MOE_TILE_N;
   const dim3 grid(max_tiles, (N + per_block - 1) / per_block);
@@ -446,7 +459,7 @@ extern "C" int sb_moe_product(const void* A, const int* row_pair, int pair_div, 
                            (int)moe_product_smem<T_>());                                                        \
     sb_launch(moe_product_kernel<T_, G_>, grid, 256, moe_product_smem<T_>(), stream, (const T_*)A, row_pair,    \
               pair_div, (const T_*)W, stride, G_ ? N : MOE_TILE_N, K, N, tile_expert, tile_row0, tile_rows,     \
-              act, (T_*)out);                                                                                   \
+              act, limit, (T_*)out);                                                                            \
   } while (0)
   if (dtype == SB_DTYPE_F32) {
     if (gated) SB_MOE_PRODUCT(float, true);
@@ -540,7 +553,7 @@ __global__ void __launch_bounds__(256) activate_rows_kernel(bf16* __restrict__ h
 // activation in place, the library's product.
 extern "C" int sb_experts_dense_bf16(const void* xs, const void* gate_up, const void* down, void* h, void* y,
                                      const int* starts, const int* counts, const int* experts, int num, int width,
-                                     int hidden, int act, int gated, int blocks, int pairs, void* workspace,
+                                     int hidden, int act, float limit, int gated, int blocks, int pairs, void* workspace,
                                      void* workspace2, long long workspace_bytes, int* done, int* err,
                                      cudaStream_t stream) {
   *done = 0;
@@ -576,7 +589,7 @@ extern "C" int sb_experts_dense_bf16(const void* xs, const void* gate_up, const 
     const bf16* dn = (const bf16*)down + (size_t)experts[i] * width * hidden;
     int rc;
     if (gated) {
-      rc = sb_gemm_gated_tc(x_i, gu, h_i, counts[i], hidden, width, act, 0.f, blocks, pairs, err, stream);
+      rc = sb_gemm_gated_tc(x_i, gu, h_i, counts[i], hidden, width, act, limit, blocks, pairs, err, stream);
       if (rc != 0) return rc;
     } else {
       rc = sb_gemm_library_bf16(x_i, gu, h_i, counts[i], hidden, width, 0, workspace, workspace_bytes, stream);

@@ -250,7 +250,7 @@ class CudaOps:
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_paged_attention_general": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void,
-                                       c_int, c_int, c_int, c_int, c_void, c_void, c_void],
+                                       c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_void],
         "sb_qk_norm_rotate_store": [c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_void, c_int, c_void,
                                     c_void, c_void, c_void, c_int, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_int, c_void, c_void],
@@ -266,7 +266,7 @@ class CudaOps:
                                c_void],
         "sb_normed_mean": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_float,
                            c_int, c_int, c_void, c_void],
-        "sb_rotate_headnorm_store": [c_void, c_int, c_int, c_float, c_float, c_void, c_int, c_int, c_int, c_int,
+        "sb_rotate_headnorm_store": [c_void, c_int, c_int, c_void, c_float, c_float, c_void, c_int, c_int, c_int, c_int,
                                      c_void, c_void, c_void, c_int, c_void, c_void, c_int, c_int, c_int, c_int,
                                      c_int, c_int, c_int, c_int, c_void, c_void],
         "sb_sigmoid_gate": [c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_void],
@@ -294,11 +294,17 @@ class CudaOps:
                                 c_void, c_void],
         "sb_forget_scan": [c_void, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_void, c_void, c_void, c_void],
-        "sb_moe_route": [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_int, c_int, c_float, c_int, c_int,
+        "sb_moe_route": [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_int, c_int, c_float, c_int, c_int,
                          c_void, c_void, c_void, c_void],
         "sb_moe_group": [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void],
         "sb_moe_product": [c_void, c_void, c_int, c_void, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_int,
-                           c_int, c_void, c_void],
+                           c_int, c_float, c_void, c_void],
+        "sb_scaled_residual_tanh": [c_void, c_void, c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void,
+                                    c_void, c_int, c_int, c_int, c_void, c_void],
+        "sb_pack_pair": [c_void, c_void, c_void, c_int, c_int, c_int, c_void],
+        "sb_add_row": [c_void, c_void, c_int, c_int, c_void],
+        "sb_xielu": [c_void, c_void, c_void, c_int, c_ll, c_void],
+        "sb_scale_values": [c_void, c_float, c_ll, c_void],
         "sb_moe_combine": [c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
                            c_void, c_void],
         "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void, c_void],
@@ -317,7 +323,8 @@ class CudaOps:
     self.lib.sb_gemm_library_bf16_heads.restype = c_int
     c_ip = ctypes.POINTER(c_int)
     self.lib.sb_experts_dense_bf16.argtypes = [c_void, c_void, c_void, c_void, c_void, c_ip, c_ip, c_ip, c_int, c_int,
-                                               c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_ll, c_ip, c_void, c_void]
+                                               c_int, c_int, c_float, c_int, c_int, c_int, c_void, c_void, c_ll, c_ip, c_void,
+                                               c_void]
     self.lib.sb_experts_dense_bf16.restype = c_int
     self.lib.sb_graph_burst.argtypes = [c_void, c_void, c_void, c_ll, c_int, c_void, c_void, c_ll, c_void]
     self.lib.sb_graph_burst.restype = c_int
@@ -727,8 +734,14 @@ class CudaOps:
         return out
     return self.gated_activation(self.linear(x, w_gate_up), activation, limit)
 
-  def lm_head(self, x: torch.Tensor, table: torch.Tensor, cap: float) -> torch.Tensor:
-    """float32 logits [R, vocab] = softcap(x . table^T)."""
+  def lm_head(self, x: torch.Tensor, table: torch.Tensor, cap: float, scale: float = 1.0) -> torch.Tensor:
+    """float32 logits [R, vocab] = softcap(scale * x . table^T)."""
+    if scale != 1.0:
+      out = self.lm_head(x, table, 0.0)
+      self._call("sb_scale_values", _ptr(out), float(scale), out.numel())
+      if cap:
+        self._call("sb_soft_cap", _ptr(out), float(cap), out.numel())
+      return out
     r, k = x.shape
     v = table.shape[0]
     out = self._new(r, v, dtype=torch.float32)
@@ -814,6 +827,58 @@ class CudaOps:
   def add_to_residual(self, h: torch.Tensor, x: torch.Tensor) -> None:
     self._call("sb_add_to_residual", _ptr(h), _ptr(x), _code(x), h.numel())
 
+  # ---- a stream whose norm computes no statistics ------------------------------------------
+  def scaled_residual_tanh(self, h: torch.Tensor, branch: torch.Tensor | None, scale: torch.Tensor | None,
+                           branch2: torch.Tensor | None, scale2: torch.Tensor | None, pre: Any,
+                           rows: torch.Tensor | None) -> torch.Tensor | None:
+    """h += scale * branch + scale2 * branch2 (float32 [width] factors; None: the branch as it is);
+    returns tanh(alpha h) w + b for the norm `pre` (its float32 `alpha` [1], `weight`, `bias`) in the
+    activation dtype, or None without one.  With `rows` only those rows are computed and h is left
+    as it is (csrc/stream_pointwise.cu)."""
+    if h.dtype != torch.float32:
+      h = self.cast(h, torch.float32)
+    width = h.shape[1]
+    if branch is None and branch2 is not None:
+      branch, scale, branch2, scale2 = branch2, scale2, None, None
+    if branch is None and pre is None:
+      return None
+    if branch is not None and branch.dtype != self.dtype:
+      branch = self.cast(branch, self.dtype)
+    if branch2 is not None and branch2.dtype != self.dtype:
+      branch2 = self.cast(branch2, self.dtype)
+    num_rows = h.shape[0] if rows is None else rows.numel()
+    y = self._new(num_rows, width) if pre is not None else None
+    self._call("sb_scaled_residual_tanh", _ptr(h), _ptr(branch), _ptr(scale), _ptr(branch2), _ptr(scale2),
+               _BF16 if self.dtype == torch.bfloat16 else _F32, _ptr(pre.alpha) if pre is not None else None,
+               _ptr(pre.weight) if pre is not None else None, _ptr(pre.bias) if pre is not None else None,
+               _ptr(rows), _ptr(y), num_rows, width, h.shape[0], _ptr(self.err))
+    return y
+
+  def scale_channels(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x * w with a float32 factor per channel, in the activation dtype."""
+    h = torch.zeros(x.shape, dtype=torch.float32, device=self.device)
+    self.scaled_residual_tanh(h, x, w, None, None, None, None)
+    return self.cast(h, self.dtype)
+
+  def pack_pair(self, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """[a, b] side by side, float32 [T, W] each, as [T, 2 W] in the activation dtype."""
+    out = self._new(a.shape[0], 2 * a.shape[1])
+    self._call("sb_pack_pair", _ptr(a), _ptr(b), _ptr(out), _code(out), a.shape[0], a.shape[1])
+    return out
+
+  def linear_wide(self, x: torch.Tensor, w: torch.Tensor, row: torch.Tensor | None = None) -> torch.Tensor:
+    """x . w^T (+ row) with float32 sums left as they are: float32 [M, N]."""
+    out = self.lm_head(x, w, 0.0)
+    if row is not None:
+      self._call("sb_add_row", _ptr(out), _ptr(row), out.shape[0], out.shape[1])
+    return out
+
+  def linear_xielu(self, x: torch.Tensor, w: torch.Tensor, act: torch.Tensor) -> torch.Tensor:
+    """xielu(x . w^T) with the activation's two learned numbers `act` (float32 [2])."""
+    z = self.linear(x, w)
+    self._call("sb_xielu", _ptr(z), _ptr(act), _ptr(z), _code(z), z.numel())
+    return z
+
   # ---- positions ------------------------------------------------------------
   def rotation_tables(self, positions: torch.Tensor, timescale: torch.Tensor, scale_factor: float):
     t, half = positions.numel(), timescale.numel()
@@ -882,19 +947,24 @@ class CudaOps:
   def paged_attention(self, q: torch.Tensor, storage: torch.Tensor, block_table: torch.Tensor, ctx: Any, *,
                       num_heads: int, num_kv_heads: int, head_dim: int, logit_softcap: float,
                       window: int | None, value_dim: int | None = None, pooled: tuple | None = None,
-                      values_in_keys: bool = False, sink: torch.Tensor | None = None) -> torch.Tensor:
+                      values_in_keys: bool = False, sink: torch.Tensor | None = None,
+                      distance_bias: torch.Tensor | None = None) -> torch.Tensor:
     """`value_dim`: size of a value head where it is not the key heads'.  `pooled`: (storage of block
     entries, its block table, block length): with a window, one key and value per whole block that
     has left the window, under the same softmax.  `values_in_keys`: an entry's value is the first
     `value_dim` numbers of its key row (a cache of latents).  `sink`: float32 [heads], a number per
-    head whose exponential joins the softmax's denominator (csrc/attention_generic.cu)."""
+    head whose exponential joins the softmax's denominator (csrc/attention_generic.cu).
+    `distance_bias`: float32 [2, heads], r1 and r2 per head: the score of query i and key j loses
+    r1 log(1 + r2 (i - j))."""
     t = q.shape[0]
     value_dim = head_dim if value_dim is None else value_dim
     out = self._new(t, num_heads * value_dim, dtype=q.dtype)
     group = num_heads // num_kv_heads
     if (values_in_keys or sink is not None) and (logit_softcap or pooled is not None):
       raise KernelError("latent rows and sinks go with neither a score cap nor pooled blocks")
-    if pooled is not None or value_dim != head_dim or values_in_keys or sink is not None:
+    if distance_bias is not None and (pooled is not None or values_in_keys):
+      raise KernelError("a distance bias goes with neither pooled blocks nor latent rows")
+    if pooled is not None or value_dim != head_dim or values_in_keys or sink is not None or distance_bias is not None:
       pool, pool_table, pool_len = pooled if pooled is not None else (None, None, 0)
       if pool is not None and pool.dtype != storage.dtype:
         raise KernelError("block entries and the cache must share one dtype")
@@ -905,7 +975,7 @@ class CudaOps:
         self._call("sb_paged_attention_general", _ptr(q), _code(q), _ptr(storage), _ptr(block_table),
                    block_table.shape[1], _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(out), t, num_heads,
                    num_kv_heads, head_dim, value_dim, ctx.page_size, storage.shape[0], float(logit_softcap),
-                   int(window or 0), *pool_args, int(values_in_keys), _ptr(sink), _ptr(self.err))
+                   int(window or 0), *pool_args, int(values_in_keys), _ptr(sink), _ptr(distance_bias), _ptr(self.err))
 
       # bfloat16 with key size = value size: the tensor-core tile kernel (mma.sync tiles of 64 rows,
       # the block entries in tiles of their own ahead of the tokens) for prompt portions and single
@@ -1036,18 +1106,21 @@ class CudaOps:
   def rotate_headnorm_store(self, proj: torch.Tensor, eps: float, q_scale: float, rot_freq: torch.Tensor | None, *,
                             interleaved: bool, head_norm: bool, tie_values: bool, num_heads: int, num_kv_heads: int,
                             head_dim: int, storage: torch.Tensor | None, block_table: torch.Tensor,
-                            ctx: Any) -> torch.Tensor:
+                            ctx: Any, value_dim: int | None = None, bias: torch.Tensor | None = None) -> torch.Tensor:
     """proj [T, q | k | (v) | ...] -> queries [T, num_heads, head_dim], rotated, each head divided by
     its root mean square, times `q_scale`; keys (rotated, normed) and values (the keys as projected
-    when `tie_values`, else the v columns) go into the pages of `storage` (csrc/attention_prepare.cu)."""
+    when `tie_values`, else the v columns) go into the pages of `storage` (csrc/attention_prepare.cu).
+    `value_dim`: size of a value head where it is not the key heads'.  `bias`: float32 offsets of the
+    q, k and v columns, added before the rotation."""
     t = proj.shape[0]
+    value_dim = head_dim if value_dim is None else value_dim
     q = self._new(t, num_heads, head_dim, dtype=proj.dtype)
     if storage is not None and storage.dtype != proj.dtype:
       raise KernelError("cache and activations must share one dtype")
-    self._call("sb_rotate_headnorm_store", _ptr(proj), proj.shape[1], _code(proj), float(eps), float(q_scale),
+    self._call("sb_rotate_headnorm_store", _ptr(proj), proj.shape[1], _code(proj), _ptr(bias), float(eps), float(q_scale),
                _ptr(rot_freq), 2 * rot_freq.numel() if rot_freq is not None else 0, int(interleaved), int(head_norm),
                int(tie_values), _ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1],
-               _ptr(ctx.token_seq), _ptr(ctx.positions), t, num_heads, num_kv_heads, head_dim, head_dim,
+               _ptr(ctx.token_seq), _ptr(ctx.positions), t, num_heads, num_kv_heads, head_dim, value_dim,
                ctx.page_size, storage.shape[0] if storage is not None else 0, int(storage is not None),
                _ptr(self.err))
     return q
@@ -1213,7 +1286,7 @@ class CudaOps:
 
   def route_tokens(self, x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None,
                    shared_gate_w: torch.Tensor | None, *, top: int, scale: float, score: int = 0,
-                   renormalize: bool = False):
+                   renormalize: bool = False, bias: torch.Tensor | None = None):
     """Per token the `top` chosen experts (int32 [T, top]), their weights (float32 [T, top]) and the
     shared expert's gate (float32 [T], or None)."""
     t, width = x.shape
@@ -1221,7 +1294,7 @@ class CudaOps:
     weight = self._new(t, top, dtype=torch.float32)
     gate = self._new(t, dtype=torch.float32) if shared_gate_w is not None else None
     self._call("sb_moe_route", _ptr(x), _code(x), t, width, _ptr(router), _ptr(correction), _ptr(shared_gate_w),
-               router.shape[0], top, float(scale), int(score), int(renormalize), _ptr(chosen), _ptr(weight), _ptr(gate))
+               _ptr(bias), router.shape[0], top, float(scale), int(score), int(renormalize), _ptr(chosen), _ptr(weight), _ptr(gate))
     return chosen, weight, gate
 
   def route_by_table(self, token_ids: torch.Tensor, table: torch.Tensor, num_experts: int):
@@ -1233,7 +1306,8 @@ class CudaOps:
                _ptr(weight), t, _ptr(self.err))
     return chosen, weight
 
-  def _experts_one_by_one(self, x, sorted_pair, tiles, top, gate_up, down, activation, gated=True) -> torch.Tensor:
+  def _experts_one_by_one(self, x, sorted_pair, tiles, top, gate_up, down, activation, gated=True,
+                          limit: float = 0.0) -> torch.Tensor:
     """The experts' products of a long prompt portion: the rows, sorted by expert, are gathered once,
     the host reads how many each expert got (the one wait of the step), and every expert's rows go
     through the engine's own products for a dense feed-forward (the tcgen05 kernel with the
@@ -1273,7 +1347,7 @@ class CudaOps:
       as_ints = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))
       rc = self.lib.sb_experts_dense_bf16(
           _ptr(xs), _ptr(gate_up), _ptr(down), _ptr(h), _ptr(y), as_ints(starts), as_ints(counts), as_ints(which),
-          len(which), width, hidden, activation, int(gated), self.gated_tc_blocks, int(self.gated_tc_pairs), _ptr(workspace),
+          len(which), width, hidden, activation, float(limit), int(gated), self.gated_tc_blocks, int(self.gated_tc_pairs), _ptr(workspace),
           _ptr(second), workspace.numel(), ctypes.byref(finished), _ptr(self.err), stream)
       if rc > 0:
         raise KernelError(f"sb_experts_dense_bf16: CUDA or cuBLAS status {rc}")
@@ -1283,13 +1357,13 @@ class CudaOps:
       self.launches += (2 if gated else 3) * done
       rest += list(zip(which[done:].tolist(), starts[done:].tolist(), counts[done:].tolist()))
     for e, start, n in rest:
-      h_e = self.gated_linear(xs[start:start + n], gate_up[e], activation)
+      h_e = self.gated_linear(xs[start:start + n], gate_up[e], activation, limit)
       y[start:start + n] = self.linear(h_e, down[e])
     return y
 
   def mix_experts(self, x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, gate_up: torch.Tensor | None,
                   down: torch.Tensor | None, num_experts: int, activation: int, shared: torch.Tensor | None,
-                  shared_gate: torch.Tensor | None, gated: bool = True) -> torch.Tensor:
+                  shared_gate: torch.Tensor | None, gated: bool = True, limit: float = 0.0) -> torch.Tensor:
     """sum_j weight[t, j] * expert(chosen[t, j])(x[t]) + shared_gate[t] * shared[t]; experts with an
     index >= num_experts return their input.  gate_up [E, 2F, W], down [E, W, F]; `gated` False:
     experts without a gate, W_down act(W_up x), with gate_up [E, F, W]."""
@@ -1311,14 +1385,14 @@ class CudaOps:
       # (whole 16-byte groups per row, so that an expert's slice of the rows starts on a boundary)
       if (x.dtype == torch.bfloat16 and 0 < self.expert_rows_for_dense_products * num_experts <= pairs
           and width % 8 == 0 and hidden % 8 == 0 and not torch.cuda.is_current_stream_capturing()):
-        y_pair = self._experts_one_by_one(x, sorted_pair, tiles, top, gate_up, down, activation, gated)
+        y_pair = self._experts_one_by_one(x, sorted_pair, tiles, top, gate_up, down, activation, gated, limit)
       else:
         h = self._new(pairs, hidden, dtype=x.dtype)
         self._call("sb_moe_product", _ptr(x), _ptr(sorted_pair), top, _ptr(gate_up), _code(x), int(gated), width, hidden,
-                   _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, activation, _ptr(h))
+                   _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, activation, float(limit), _ptr(h))
         y_pair = self._new(pairs, width, dtype=x.dtype)
         self._call("sb_moe_product", _ptr(h), None, 1, _ptr(down), _code(x), 0, hidden, width,
-                   _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, -1, _ptr(y_pair))
+                   _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, -1, 0.0, _ptr(y_pair))
     else:
       pos.fill_(-1)
     if shared is not None and shared.dtype != x.dtype:
