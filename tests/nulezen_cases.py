@@ -81,7 +81,7 @@ CONFIG_D = config([rotated(heads=2, kv_heads=1, dim=16, vdim=16, dims=16, window
                   [dense(ff=32), moe(experts=4, top=2, ff=12)], width=32, vocab=60, loop=(0, 2, 3))
 
 
-def weights(cfg_dict, seed=0, matrix_std=0.25, scale_std=0.2):
+def weights(cfg_dict, seed=0, matrix_std=0.18, scale_std=0.2):
   """bfloat16-representable random weights by tensor name (CPU, bfloat16)."""
   cfg = config_from_dict(cfg_dict)
   specs = DecoderModel(cfg.model_spec()).tensor_specs()
