@@ -52,6 +52,9 @@ struct AttnParams {
   int num_q_heads, num_kv_heads, page_size, num_pages;
   float cap;
   int window;
+  // optional, float32 [2, Hq]: r1 and r2 per query head; the score of query i and key j loses
+  // r1 log(1 + r2 (i - j))
+  const float* distance;
   const int* items;  // prefill: (sequence, first token of the tile); decode: (sequence, chunk)
   int chunk;         // decode: keys per chunk (a multiple of BN)
   float* part_o;     // decode: [items, Hkv, rows_max, DH]
@@ -202,11 +205,29 @@ __device__ __forceinline__ void scores(float (&s)[NKT][4], const bf16* sq_rows, 
 // Soft cap, mask, online softmax update and P.V for one warp.  `pos_a`, `pos_b`: positions of
 // the thread's two query rows (-1 for a padding row).  `j0`: position of the first of the
 // NKT * 8 keys.  m_* are kept in log2 units.
+// The distance bias of one query row: r1 ln 2 and r2 of its head (zeros: none).
+struct RowBias {
+  float r1, r2;
+};
+__device__ __forceinline__ RowBias row_bias(const float* distance, int num_q_heads, int head) {
+  RowBias b{0.f, 0.f};
+  if (distance != nullptr) {
+    b.r1 = distance[head] * 0.6931471805599453f;
+    b.r2 = distance[num_q_heads + head];
+  }
+  return b;
+}
+// r1 ln(1 + r2 d) for d >= 0 keys between the query and the key.
+__device__ __forceinline__ float distance_loss(const RowBias& b, int d) {
+  return b.r1 * __log2f(fmaf(b.r2, (float)max(d, 0), 1.0f));
+}
+
 template <int NKT>
 __device__ __forceinline__ void softmax_pv(float (&s)[NKT][4], float (&o)[DH / 8][4], float& m_a, float& m_b,
                                            float& l_a, float& l_b, int pos_a, int pos_b, int j0, float cap,
                                            int window, const bf16* sv, int key0, bool need_mask = true,
-                                           int pool_len = 0) {
+                                           int pool_len = 0, bool biased = false, RowBias bias_a = RowBias{0.f, 0.f},
+                                           RowBias bias_b = RowBias{0.f, 0.f}) {
   // pool_len > 0: the keys are block entries j0, j0 + 1, ...; a row at `pos` sees the blocks that
   // lie wholly before its window, j < (pos - window + 1) / pool_len.
   const int lane = threadIdx.x & 31, t = lane & 3;
@@ -220,6 +241,7 @@ __device__ __forceinline__ void softmax_pv(float (&s)[NKT][4], float (&o)[DH / 8
       const int pos = e < 2 ? pos_a : pos_b;
       float v = s[i][e];
       if (cap > 0.f) v = cap * fast_tanh(v * inv_cap);
+      if (biased) v -= distance_loss(e < 2 ? bias_a : bias_b, pos - j);
       // need_mask is false (for the whole warp) when every key of the tile is visible to every row.
       const bool keep = pool_len > 0 ? (pos - window + 1 > 0 && j < (pos - window + 1) / pool_len)
                                      : (!need_mask || (j <= pos && (window <= 0 || pos - j < window)));
@@ -328,6 +350,9 @@ __global__ void __launch_bounds__(WM * WN * 32) attn_prefill_kernel(const AttnPa
   const int pos_a = ra < rows_valid ? p0 + ra / group : -1;
   const int pos_b = rb < rows_valid ? p0 + rb / group : -1;
   // Positions of this warp's first and last row, for deciding whether a tile needs masking.
+  const bool biased = p.distance != nullptr;
+  const RowBias bias_a = row_bias(p.distance, p.num_q_heads, m * group + ra % group);
+  const RowBias bias_b = row_bias(p.distance, p.num_q_heads, m * group + rb % group);
   const bool rows_full = wm * 16 + 15 < rows_valid;
   const int warp_pos_lo = p0 + (wm * 16) / group, warp_pos_hi = p0 + (wm * 16 + 15) / group;
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
@@ -354,7 +379,7 @@ __global__ void __launch_bounds__(WM * WN * 32) attn_prefill_kernel(const AttnPa
     float s[KEYS / 8][4];
     scores<KEYS / 8>(s, sq + wm * 16 * PITCH, sk + stage * BN * PITCH, wn * KEYS);
     softmax_pv<KEYS / 8>(s, o, m_a, m_b, l_a, l_b, pos_a, pos_b, j0, p.cap, p.window, sv + stage * BN * PITCH,
-                         wn * KEYS, need_mask, pooled ? p.pool_len : 0);
+                         wn * KEYS, need_mask, pooled ? p.pool_len : 0, biased && !pooled, bias_a, bias_b);
     __syncthreads();
   }
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
@@ -466,6 +491,8 @@ __global__ void __launch_bounds__(DEC_NT) attn_decode_kernel(const AttnParams p,
     }
     const int pos_a = g < rows_valid ? qs + g / group : -1;
     const int pos_b = g + 8 < rows_valid ? qs + (g + 8) / group : -1;
+    const RowBias bias_a = row_bias(p.distance, p.num_q_heads, m * group + g % group);
+    const RowBias bias_b = row_bias(p.distance, p.num_q_heads, m * group + (g + 8) % group);
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     float o[DH / 8][4];
 #pragma unroll
@@ -484,7 +511,7 @@ __global__ void __launch_bounds__(DEC_NT) attn_decode_kernel(const AttnParams p,
       float s[2][4];
       scores<2>(s, sq, sk + stage * DEC_BN * PITCH, warp * 16);
       softmax_pv<2>(s, o, m_a, m_b, l_a, l_b, pos_a, pos_b, begin + it * DEC_BN + warp * 16, p.cap, p.window,
-                    sv + stage * DEC_BN * PITCH, warp * 16);
+                    sv + stage * DEC_BN * PITCH, warp * 16, true, 0, p.distance != nullptr, bias_a, bias_b);
     }
     cp_async_wait<0>();
     __syncthreads();
@@ -731,6 +758,9 @@ attn_decode8_kernel(const AttnParams p, int* work_counter, int total_work, const
     const int pos0 = 2 * t < rows_valid ? qs + (2 * t) / group : -1;
     const int pos1 = 2 * t + 1 < rows_valid ? qs + (2 * t + 1) / group : -1;
     const float inv_cap = p.cap > 0.f ? 1.0f / p.cap : 0.f;
+    const bool biased = p.distance != nullptr;
+    const RowBias bias0 = row_bias(p.distance, p.num_q_heads, m * group + (2 * t) % group);
+    const RowBias bias1 = row_bias(p.distance, p.num_q_heads, m * group + (2 * t + 1) % group);
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     float o[DH / 16][4];  // out^T: [dims 16 blk + g | g + 8][rows 2t | 2t + 1]
 #pragma unroll
@@ -789,6 +819,7 @@ attn_decode8_kernel(const AttnParams p, int* work_counter, int total_work, const
           if (p.cap > 0.f) v = p.cap * fast_tanh(v * inv_cap);
           const int j = j_first + g + (e >> 1) * 8;
           const int pos = (e & 1) ? pos1 : pos0;
+          if (biased) v -= distance_loss((e & 1) ? bias1 : bias0, pos - j);
           const bool keep = j <= pos && (p.window <= 0 || pos - j < p.window);
           sc[e] = keep ? v * LOG2E : -INFINITY;
         }
@@ -1072,6 +1103,9 @@ attn_decode8ws_kernel(const AttnParams p, int* work_counter, int total_work, con
     const int pos0 = 2 * t < rows_valid ? w.qs + (2 * t) / group : -1;
     const int pos1 = 2 * t + 1 < rows_valid ? w.qs + (2 * t + 1) / group : -1;
     const float inv_cap = p.cap > 0.f ? 1.0f / p.cap : 0.f;
+    const bool biased = p.distance != nullptr;
+    const RowBias bias0 = row_bias(p.distance, p.num_q_heads, w.m * group + (2 * t) % group);
+    const RowBias bias1 = row_bias(p.distance, p.num_q_heads, w.m * group + (2 * t + 1) % group);
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     float o[DH / 16][4];
 #pragma unroll
@@ -1117,6 +1151,7 @@ attn_decode8ws_kernel(const AttnParams p, int* work_counter, int total_work, con
         if (p.cap > 0.f) v = p.cap * fast_tanh(v * inv_cap);
         const int j = j_first + g + (e >> 1) * 8;
         const int pos = (e & 1) ? pos1 : pos0;
+        if (biased) v -= distance_loss((e & 1) ? bias1 : bias0, pos - j);
         const bool keep = j <= pos && (p.window <= 0 || pos - j < p.window);
         sc[e] = keep ? v * LOG2E : -INFINITY;
       }
@@ -1331,16 +1366,18 @@ static int blocks_resident(Kernel kernel, int threads, size_t smem, int* out) {
 // rows_per_tile / G tokens); rows_per_tile is 64 or 128.  Tiles of 64 rows run with two key
 // groups (8 warps) unless single_key_group is set.
 // With `pool`: block entries of `pool_len` tokens ahead of the window (see AttnParams).
-extern "C" int SB_FN(sb_attn_prefill_pooled)(const void* q, const void* cache, const int* block_table, int max_pages,
-                                             const int* cu_q, const int* q_start, void* out, int num_q_heads,
-                                             int num_kv_heads, int page_size, int num_pages, float cap, int window,
-                                             const int* items, int num_items, int rows_per_tile, int single_key_group,
-                                             const void* pool, const int* pool_table, int pool_max_pages, int pool_len,
-                                             int pool_pages, int* err, cudaStream_t stream) {
+static int prefill_launch(const void* q, const void* cache, const int* block_table, int max_pages,
+                          const int* cu_q, const int* q_start, void* out, int num_q_heads,
+                          int num_kv_heads, int page_size, int num_pages, float cap, int window,
+                          const float* distance,
+                          const int* items, int num_items, int rows_per_tile, int single_key_group,
+                          const void* pool, const int* pool_table, int pool_max_pages, int pool_len,
+                          int pool_pages, int* err, cudaStream_t stream) {
   if (num_items == 0) return 0;
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads || num_q_heads / num_kv_heads > rows_per_tile) return -8;
   if (pool != nullptr && (pool_len <= 0 || window <= 0)) return -8;
   AttnParams p{};
+  p.distance = distance;
   p.q = (const bf16*)q; p.cache = (const bf16*)cache; p.block_table = block_table; p.max_pages = max_pages;
   p.cu_q = cu_q; p.q_start = q_start; p.out = (bf16*)out; p.num_q_heads = num_q_heads;
   p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages; p.cap = cap;
@@ -1388,9 +1425,31 @@ extern "C" int SB_FN(sb_attn_prefill)(const void* q, const void* cache, const in
                                       int num_kv_heads, int page_size, int num_pages, float cap, int window,
                                       const int* items, int num_items, int rows_per_tile, int single_key_group,
                                       int* err, cudaStream_t stream) {
-  return SB_FN(sb_attn_prefill_pooled)(q, cache, block_table, max_pages, cu_q, q_start, out, num_q_heads, num_kv_heads,
-                                       page_size, num_pages, cap, window, items, num_items, rows_per_tile,
-                                       single_key_group, nullptr, nullptr, 0, 0, 0, err, stream);
+  return prefill_launch(q, cache, block_table, max_pages, cu_q, q_start, out, num_q_heads, num_kv_heads, page_size,
+                        num_pages, cap, window, nullptr, items, num_items, rows_per_tile, single_key_group, nullptr,
+                        nullptr, 0, 0, 0, err, stream);
+}
+
+extern "C" int SB_FN(sb_attn_prefill_pooled)(const void* q, const void* cache, const int* block_table, int max_pages,
+                                             const int* cu_q, const int* q_start, void* out, int num_q_heads,
+                                             int num_kv_heads, int page_size, int num_pages, float cap, int window,
+                                             const int* items, int num_items, int rows_per_tile, int single_key_group,
+                                             const void* pool, const int* pool_table, int pool_max_pages, int pool_len,
+                                             int pool_pages, int* err, cudaStream_t stream) {
+  return prefill_launch(q, cache, block_table, max_pages, cu_q, q_start, out, num_q_heads, num_kv_heads, page_size,
+                        num_pages, cap, window, nullptr, items, num_items, rows_per_tile, single_key_group, pool,
+                        pool_table, pool_max_pages, pool_len, pool_pages, err, stream);
+}
+
+// The same with a distance bias: `distance` float32 [2, Hq] (see AttnParams).
+extern "C" int SB_FN(sb_attn_prefill_biased)(const void* q, const void* cache, const int* block_table, int max_pages,
+                                             const int* cu_q, const int* q_start, void* out, int num_q_heads,
+                                             int num_kv_heads, int page_size, int num_pages, float cap, int window,
+                                             const int* items, int num_items, int rows_per_tile, int single_key_group,
+                                             const float* distance, int* err, cudaStream_t stream) {
+  return prefill_launch(q, cache, block_table, max_pages, cu_q, q_start, out, num_q_heads, num_kv_heads, page_size,
+                        num_pages, cap, window, distance, items, num_items, rows_per_tile, single_key_group, nullptr,
+                        nullptr, 0, 0, 0, err, stream);
 }
 
 // Split-key attention for sequences with at most 16 query rows per kv head, and the merge.
@@ -1407,8 +1466,8 @@ extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int
                                      int num_pages, float cap, int window, const int* items, int num_items,
                                      int chunk, float* part_o, float* part_ml, int* work_counter,
                                      int rows_max, const int* split_start, const int* split_count, int variant,
-                                     const void* tensor_map, int older_keys_settled, int* err,
-                                     cudaStream_t stream) {
+                                     const void* tensor_map, int older_keys_settled, const float* distance,
+                                     int* err, cudaStream_t stream) {
   // variant: 0 picks the kernel by rows_max (<= 8: the turned-round kernel, fed by TMA through a
   // producer warp when a tensor map is given and the shapes allow); 1 forbids TMA; 2 uses TMA
   // without the producer warp; 16 forces the 16-row kernel.
@@ -1420,6 +1479,7 @@ extern "C" int SB_FN(sb_attn_decode)(const void* q, const void* cache, const int
   p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages; p.cap = cap;
   p.window = window; p.items = items; p.chunk = chunk; p.part_o = part_o; p.part_ml = part_ml;
   p.rows_max = rows_max; p.older_keys_settled = older_keys_settled; p.err = err;
+  p.distance = distance;
   const int total_work = num_items * num_kv_heads;
   const bool power_of_two_pages = (page_size & (page_size - 1)) == 0;
   constexpr size_t ws_merge = (size_t)(D8_WARPS * 8 * DH) * sizeof(float);

@@ -424,8 +424,11 @@ class CudaOps:
       decode = getattr(lib, f"sb_attn_decode_hd{head_dim}")
       decode.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_int, c_int, c_int,
                          c_int, c_int, c_float, c_int, c_void, c_int, c_int, c_void, c_void, c_void, c_int,
-                         c_void, c_void, c_int, c_void, c_int, c_void, c_void]
+                         c_void, c_void, c_int, c_void, c_int, c_void, c_void, c_void]
       decode.restype = c_int
+      prefill_biased = getattr(lib, f"sb_attn_prefill_biased_hd{head_dim}")
+      prefill_biased.argtypes = prefill.argtypes[:-2] + [c_void, c_void, c_void]
+      prefill_biased.restype = c_int
       make_map = getattr(lib, f"sb_attn_tensor_map_hd{head_dim}")
       make_map.argtypes = [c_void, c_void, ctypes.c_longlong, c_int]
       make_map.restype = c_int
@@ -447,7 +450,8 @@ class CudaOps:
       if slots <= 0:
         raise KernelError(f"sb_attn_decode_resident: {_STATUS.get(slots, slots)}")
       self._decode_slots[head_dim] = slots
-      fns = self._attn_fns[head_dim] = (prefill, decode, make_map, prefill_tc, prefill_pair, prefill_pooled)
+      fns = self._attn_fns[head_dim] = (prefill, decode, make_map, prefill_tc, prefill_pair, prefill_pooled,
+                                        prefill_biased)
     return fns
 
   def _latent_fn(self, row_dim: int, value_dim: int):
@@ -964,7 +968,11 @@ class CudaOps:
       raise KernelError("latent rows and sinks go with neither a score cap nor pooled blocks")
     if distance_bias is not None and (pooled is not None or values_in_keys):
       raise KernelError("a distance bias goes with neither pooled blocks nor latent rows")
-    if pooled is not None or value_dim != head_dim or values_in_keys or sink is not None or distance_bias is not None:
+    # (a distance bias with key size = value size in bfloat16: the mma.sync tile kernels below)
+    biased_on_tensor_cores = (distance_bias is not None and value_dim == head_dim and q.dtype == torch.bfloat16
+                              and self._uses_tensor_core_attention(head_dim, group))
+    if (pooled is not None or value_dim != head_dim or values_in_keys or sink is not None
+        or (distance_bias is not None and not biased_on_tensor_cores)):
       pool, pool_table, pool_len = pooled if pooled is not None else (None, None, 0)
       if pool is not None and pool.dtype != storage.dtype:
         raise KernelError("block entries and the cache must share one dtype")
@@ -1022,8 +1030,10 @@ class CudaOps:
       return out
     if q.dtype == torch.bfloat16 and self._uses_tensor_core_attention(head_dim, group):
       prefill, decode, _, prefill_tc, prefill_pair = self._attention_lib(head_dim)[:5]
-      use_tc = prefill_tc is not None and self._prefill_uses_tcgen05(head_dim, group, ctx.page_size)
-      use_pair = prefill_pair is not None and self._prefill_uses_pairs(head_dim, group, ctx.page_size)
+      use_tc = (prefill_tc is not None and self._prefill_uses_tcgen05(head_dim, group, ctx.page_size)
+                and distance_bias is None)
+      use_pair = (prefill_pair is not None and self._prefill_uses_pairs(head_dim, group, ctx.page_size)
+                  and distance_bias is None)
       plan = self._attention_plan(ctx, window, group, 256 if use_pair else (128 if use_tc else 0), num_kv_heads, head_dim)
       common = (_ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_q),
                 _ptr(ctx.q_start))
@@ -1040,6 +1050,16 @@ class CudaOps:
         self.launches += 1
         if rc:
           raise KernelError(f"sb_attn_prefill_tc: {_STATUS.get(rc, rc)}")
+      elif plan["num_prefill"] and distance_bias is not None:
+        tiles = plan
+        if plan["rows_per_tile"] > 128:  # (a list cut for pairs of blocks, made by a layer without a bias)
+          tiles = self._attention_plan(ctx, window, group, 64, num_kv_heads, head_dim, tag=("rows", 64))
+        rc = self._attention_lib(head_dim)[6](
+            *common, _ptr(out), *sizes, _ptr(tiles["prefill_items"]), tiles["num_prefill"], tiles["rows_per_tile"],
+            int(self.prefill_single_key_group), _ptr(distance_bias), _ptr(self.err), self._stream())
+        self.launches += 1
+        if rc:
+          raise KernelError(f"sb_attn_prefill_biased: {_STATUS.get(rc, rc)}")
       elif plan["num_prefill"]:
         rc = prefill(*common, _ptr(out), *sizes, _ptr(plan["prefill_items"]), plan["num_prefill"],
                      plan["rows_per_tile"], int(self.prefill_single_key_group), _ptr(self.err), self._stream())
@@ -1055,7 +1075,7 @@ class CudaOps:
                     plan["rows_max"],
                     _ptr(plan["split_start"]), _ptr(plan["split_count"]), self.decode_variant,
                     self._tensor_map(storage, head_dim, ctx.page_size),
-                    int(getattr(ctx, "older_keys_settled", False)), _ptr(self.err), self._stream())
+                    int(getattr(ctx, "older_keys_settled", False)), _ptr(distance_bias), _ptr(self.err), self._stream())
         self.launches += 2
         if rc:
           raise KernelError(f"sb_attn_decode: {_STATUS.get(rc, rc)}")

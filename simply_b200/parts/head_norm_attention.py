@@ -87,7 +87,7 @@ class HeadNormAttention(Mixer):
                        value_dim=None if self.value_dim == self.head_dim else self.value_dim)
 
   def graph_plans(self, ops, batch: int, bucket: int, max_burst: int, page_size: int) -> list:
-    if self.value_dim != self.head_dim or self.distance_bias:
+    if self.value_dim != self.head_dim:
       return []  # (the general kernel needs no list)
     plan = ops.attention_graph_plan(
         window=self.window, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
@@ -108,7 +108,7 @@ class HeadNormAttention(Mixer):
     return [p for p in (self.q_proj, self.k_proj, self.v_proj) if p is not None]
 
   def bind(self, tensors, ops) -> None:
-    if self.head_dim % 2 == 0 and self.value_dim == self.head_dim and not self.distance_bias:  # (the general kernel takes the rest)
+    if self.head_dim % 2 == 0 and self.value_dim == self.head_dim:  # (the general kernel takes the rest)
       ops.check_attention(self.head_dim, self.num_heads, self.num_kv_heads)
     w = fuse_rows([tensors[p.name] for p in self._inputs()])
     extra = -w.shape[0] % 8  # whole 16-byte groups of output features for the products' stores
