@@ -432,7 +432,7 @@ def profile_step(engine, torch, cfg, args, context):
 
 
 def design_arm(args):
-  """`--design generax|sapivik|zesapel`: see simply_b200/design_bench.py.  One JSON line; `value` is the
+  """`--design generax|sapivik|zesapel|nulezen`: see simply_b200/design_bench.py.  One JSON line; `value` is the
   design's decode throughput at the first size."""
   import torch
 
@@ -474,9 +474,9 @@ def main(argv=None):
   ap.add_argument("--profile", choices=["decode", "prefill", "mixed"], default=None,
                   help="run ONE eager step of this kind between cudaProfilerStart/Stop and exit "
                        "(for ncu --profile-from-start off); prints no benchmark line")
-  ap.add_argument("--design", choices=["generax", "sapivik", "zesapel"], default=None,
+  ap.add_argument("--design", choices=["generax", "sapivik", "zesapel", "nulezen"], default=None,
                   help="instead of the default workload: prefill and decode throughput of this design beside "
-                       "the engine's closest other model (Gemma 2 for generax, generax for sapivik) at equal size (layer shapes like a real model's, random weights), and every "
+                       "the engine's closest other model (Gemma 2 for generax, generax for sapivik, sapivik for zesapel and nulezen) at equal size (layer shapes like a real model's, random weights), and every "
                        "kernel call of one step of each timed alone against the measured peaks")
   args = ap.parse_args(argv)
   if args.impl == "reference":

@@ -77,6 +77,9 @@ struct TcParams {
   int num_q_heads, num_kv_heads, page_size, num_pages;
   float cap;
   int window;
+  // optional, float32 [2, Hq]: r1 and r2 per query head; the score of query i and key j loses
+  // r1 log(1 + r2 (i - j)) (not together with a cap)
+  const float* distance;
   const int* items;  // per block, in launch order: (sequence, first token of the tile of 128 / G tokens, kv head)
   int box_rows;      // rows per key/value TMA box: min(page_size, 64)
   int* err;
@@ -298,6 +301,11 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     const int warp_pos_lo = p0 + (quarter * 32) / group, warp_pos_hi = p0 + (quarter * 32 + 31) / group;
     const float inv_cap = p.cap > 0.f ? 1.0f / p.cap : 0.f;
     const float scale2 = p.cap > 0.f ? p.cap * LOG2E : LOG2E;  // from x (tanh's value, or the score) to log2 units
+    // The distance bias of this thread's row: r1 ln 2 and r2 of its head.
+    const bool biased = p.distance != nullptr;
+    const int head = m * group + (r < rows_valid ? r % group : 0);
+    const float bias_r1 = biased ? p.distance[head] * 0.6931471805599453f : 0.f;
+    const float bias_r2 = biased ? p.distance[p.num_q_heads + head] : 0.f;
     float m_own = -INFINITY, l = 0.f;  // the maximum this thread's sum is relative to; the sum
     bool ok = true;
     if (QT_DIMS > 0) {
@@ -337,6 +345,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           float v = __uint_as_float(sr[c]);
           if (p.cap > 0.f) v = fast_tanh(v * inv_cap);
           const int key = j0 + part * CW + c;
+          if (biased) v -= bias_r1 * __log2f(fmaf(bias_r2, (float)max(pos - key, 0), 1.0f));
           v = (key <= pos && (p.window <= 0 || pos - key < p.window)) ? v : -INFINITY;
           sr[c] = __float_as_uint(v);
           mx = fmaxf(mx, v);
@@ -346,6 +355,7 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
         for (int c = 0; c < CW; ++c) {
           float v = __uint_as_float(sr[c]);
           if (p.cap > 0.f) v = fast_tanh(v * inv_cap);
+          if (biased) v -= bias_r1 * __log2f(fmaf(bias_r2, (float)(pos - (j0 + part * CW + c)), 1.0f));
           sr[c] = __float_as_uint(v);
           mx = fmaxf(mx, v);
         }
@@ -526,11 +536,13 @@ static_assert(V_STAGES == 2, "the zeroing of value rows looks two tiles back");
 // which the blocks are to start (longest walk first over all heads, so that the SMs that are free
 // first take the longest walks left).  Returns -11 when
 // the shapes do not allow it (the group must divide 128, the page size must be a power of two).
-extern "C" int SB_FN(sb_attn_prefill_tc)(const void* q, const void* cache, const int* block_table, int max_pages,
-                                         const int* cu_q, const int* q_start, void* out, int num_tokens,
-                                         int num_q_heads, int num_kv_heads, int page_size, int num_pages, float cap,
-                                         int window, const int* items, int num_items, int* err, cudaStream_t stream) {
+static int prefill_tc_launch(const void* q, const void* cache, const int* block_table, int max_pages,
+                             const int* cu_q, const int* q_start, void* out, int num_tokens,
+                             int num_q_heads, int num_kv_heads, int page_size, int num_pages, float cap,
+                             int window, const float* distance, const int* items, int num_items, int* err,
+                             cudaStream_t stream) {
   if (num_items == 0) return 0;
+  if (distance != nullptr && cap > 0.f) return -13;
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads) return -8;
   const int group = num_q_heads / num_kv_heads;
   if (group > BM || BM % group || (page_size & (page_size - 1))) return -11;
@@ -554,6 +566,7 @@ extern "C" int SB_FN(sb_attn_prefill_tc)(const void* q, const void* cache, const
   p.block_table = block_table; p.max_pages = max_pages; p.cu_q = cu_q; p.q_start = q_start; p.out = (bf16*)out;
   p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
   p.cap = cap; p.window = window; p.items = items; p.box_rows = box_rows; p.err = err;
+  p.distance = distance;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
@@ -563,6 +576,25 @@ extern "C" int SB_FN(sb_attn_prefill_tc)(const void* q, const void* cache, const
   sb_launch(attn_prefill_tc_kernel, dim3(num_items), TC_THREADS, TC_SMEM, stream, p, map_q, map_kv, map_out);
   SB_LAUNCH_CHECK();
   return 0;
+}
+
+extern "C" int SB_FN(sb_attn_prefill_tc)(const void* q, const void* cache, const int* block_table, int max_pages,
+                                         const int* cu_q, const int* q_start, void* out, int num_tokens,
+                                         int num_q_heads, int num_kv_heads, int page_size, int num_pages, float cap,
+                                         int window, const int* items, int num_items, int* err, cudaStream_t stream) {
+  return prefill_tc_launch(q, cache, block_table, max_pages, cu_q, q_start, out, num_tokens, num_q_heads, num_kv_heads,
+                           page_size, num_pages, cap, window, nullptr, items, num_items, err, stream);
+}
+
+// The same with a distance bias: `distance` float32 [2, Hq] (see TcParams); no cap beside it.
+extern "C" int SB_FN(sb_attn_prefill_tc_biased)(const void* q, const void* cache, const int* block_table,
+                                                int max_pages, const int* cu_q, const int* q_start, void* out,
+                                                int num_tokens, int num_q_heads, int num_kv_heads, int page_size,
+                                                int num_pages, float cap, int window, const int* items,
+                                                int num_items, const float* distance, int* err,
+                                                cudaStream_t stream) {
+  return prefill_tc_launch(q, cache, block_table, max_pages, cu_q, q_start, out, num_tokens, num_q_heads, num_kv_heads,
+                           page_size, num_pages, cap, window, distance, items, num_items, err, stream);
 }
 
 #endif  // head sizes that are no multiple of 64 do not get this kernel

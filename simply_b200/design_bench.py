@@ -1,8 +1,8 @@
 """Prefill and decode throughput of a design beside the engine's closest other model at equal size
-(Generax beside Gemma 2, Sapivik beside Generax, Zesapel beside Sapivik), and the time of every kernel
+(Generax beside Gemma 2, Sapivik beside Generax, Zesapel beside Sapivik, Nulezen beside Sapivik), and the time of every kernel
 call of one step of each with its share of the measured peaks.
 
-Used by `bench.py --design generax|sapivik|zesapel` (the default benchmark does not import this file).  Layer
+Used by `bench.py --design generax|sapivik|zesapel|nulezen` (the default benchmark does not import this file).  Layer
 shapes resemble a real model's; weights are random.  Per size and design:
 
 * prefill: one 2,048-token prompt in one step, median of 5 after 3 warm-up steps, CUDA events;
@@ -94,6 +94,32 @@ def zesapel_dict(s: dict) -> dict:
           "layers": layers}
 
 
+def nulezen_dict(s: dict) -> dict:
+  """Windowed attention everywhere: one layer in three rotates its heads, has biases and a gate per
+  head and a dense feed-forward with the learned activation; the others take the distance bias off
+  their scores, gate every element and have routed experts of the Sapivik arm's shape (sixteen of a
+  quarter of the dense hidden size, four per token, a shared one).  The first three layers run
+  twice, as in the Sapivik arm."""
+  att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+         "scale": s["dim"] ** -0.5, "mask": {"size": WINDOW}}
+  experts = {"kind": "moe", "expert": {"ff": s["ff"] // 4, "limit": 7.0}, "shared": {"ff": s["ff"] // 4, "limit": 7.0},
+             "router": {"experts": 16, "top": 4}}
+  layers = []
+  for i in range(s["layers"]):
+    if i % 3 == 0:
+      layers.append({"type": "attention_2", "mixer": dict(att, rot={"dims": s["dim"] // 2, "base": 10000.0}),
+                     "mlp": {"kind": "dense", "ff": s["ff"]}})
+    else:
+      layers.append({"type": "attention", "mixer": dict(att), "mlp": dict(experts)})
+  times = 2
+  stop = min(3, s["layers"])
+  d = {"architecture": "Nulezen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+       "embedding": {"scale": 1.0}, "logit_scale": 1.0,
+       "layers": layers[:s["layers"] - stop * (times - 1)] if s["layers"] > stop else layers, "max_context": 8192}
+  d["loop"] = {"start": 0, "stop": stop, "times": times if s["layers"] > stop else 1}
+  return d
+
+
 def gemma2_dict(s: dict) -> dict:
   return {"architectures": ["Gemma2ForCausalLM"], "hidden_size": s["width"], "num_hidden_layers": s["layers"],
           "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": s["dim"],
@@ -140,7 +166,7 @@ class TimedOps:
       moved = sum(_nbytes(t) for t in tensors) + _nbytes(out)
       flops = 0.0
       ctx = next((a for a in list(args) + list(kw.values()) if hasattr(a, "num_tokens") and hasattr(a, "cu_q")), None)
-      if name in ("linear", "gated_linear", "lm_head"):
+      if name in ("linear", "gated_linear", "lm_head", "linear_xielu", "linear_wide"):
         x, w = args[0], args[1]
         flops = 2.0 * x.shape[0] * w.shape[0] * w.shape[1]
       if name == "mix_experts":
@@ -234,8 +260,10 @@ def _prefill_ms(engine, tokens: int, vocab: int) -> float:
   return float(np.median(times))
 
 
-PAIRS = {"generax": ("generax", "gemma2"), "sapivik": ("sapivik", "generax"), "zesapel": ("zesapel", "sapivik")}
-DICTS = {"generax": generax_dict, "gemma2": gemma2_dict, "sapivik": sapivik_dict, "zesapel": zesapel_dict}
+PAIRS = {"generax": ("generax", "gemma2"), "sapivik": ("sapivik", "generax"), "zesapel": ("zesapel", "sapivik"),
+         "nulezen": ("nulezen", "sapivik")}
+DICTS = {"generax": generax_dict, "gemma2": gemma2_dict, "sapivik": sapivik_dict, "zesapel": zesapel_dict,
+         "nulezen": nulezen_dict}
 
 
 def run(args, peaks: dict, time_decode, design: str = "generax") -> dict:

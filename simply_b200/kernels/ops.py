@@ -432,12 +432,15 @@ class CudaOps:
       make_map = getattr(lib, f"sb_attn_tensor_map_hd{head_dim}")
       make_map.argtypes = [c_void, c_void, ctypes.c_longlong, c_int]
       make_map.restype = c_int
-      prefill_tc = None
+      prefill_tc = prefill_tc_biased = None
       if head_dim % 64 == 0:
         prefill_tc = getattr(lib, f"sb_attn_prefill_tc_hd{head_dim}")
         prefill_tc.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
                                c_int, c_float, c_int, c_void, c_int, c_void, c_void]
         prefill_tc.restype = c_int
+        prefill_tc_biased = getattr(lib, f"sb_attn_prefill_tc_biased_hd{head_dim}")
+        prefill_tc_biased.argtypes = prefill_tc.argtypes[:-2] + [c_void, c_void, c_void]
+        prefill_tc_biased.restype = c_int
       prefill_pair = None
       if head_dim in (128, 256):
         prefill_pair = getattr(lib, f"sb_attn_prefill_pair_hd{head_dim}")
@@ -451,7 +454,7 @@ class CudaOps:
         raise KernelError(f"sb_attn_decode_resident: {_STATUS.get(slots, slots)}")
       self._decode_slots[head_dim] = slots
       fns = self._attn_fns[head_dim] = (prefill, decode, make_map, prefill_tc, prefill_pair, prefill_pooled,
-                                        prefill_biased)
+                                        prefill_biased, prefill_tc_biased)
     return fns
 
   def _latent_fn(self, row_dim: int, value_dim: int):
@@ -643,7 +646,7 @@ class CudaOps:
     n_pre, n_dec = prefill_items.size, decode_items.size
     plan = dict(
         num_prefill=len(prefill_items), num_decode=len(decode_items), chunk=chunk, rows_per_tile=rows_per_tile,
-        rows_max=int((q_len[dec] * group).max()) if len(dec) else 0,
+        item_width=prefill_items.shape[1], rows_max=int((q_len[dec] * group).max()) if len(dec) else 0,
         prefill_items=dev[:n_pre], decode_items=dev[n_pre:n_pre + n_dec],
         split_start=dev[n_pre + n_dec:n_pre + n_dec + num_seqs], split_count=dev[n_pre + n_dec + num_seqs:])
     ctx.memo[key] = plan
@@ -1030,8 +1033,10 @@ class CudaOps:
       return out
     if q.dtype == torch.bfloat16 and self._uses_tensor_core_attention(head_dim, group):
       prefill, decode, _, prefill_tc, prefill_pair = self._attention_lib(head_dim)[:5]
+      # A distance bias: the tcgen05 kernel by single blocks where it takes the shape (no cap beside
+      # it), else the mma.sync tile kernel; not the kernel by pairs.
       use_tc = (prefill_tc is not None and self._prefill_uses_tcgen05(head_dim, group, ctx.page_size)
-                and distance_bias is None)
+                and (distance_bias is None or not logit_softcap))
       use_pair = (prefill_pair is not None and self._prefill_uses_pairs(head_dim, group, ctx.page_size)
                   and distance_bias is None)
       plan = self._attention_plan(ctx, window, group, 256 if use_pair else (128 if use_tc else 0), num_kv_heads, head_dim)
@@ -1044,6 +1049,15 @@ class CudaOps:
         self.launches += 1
         if rc:
           raise KernelError(f"sb_attn_prefill_pair: {_STATUS.get(rc, rc)}")
+      elif plan["num_prefill"] and use_tc and distance_bias is not None:
+        tiles = plan
+        if plan["rows_per_tile"] != 128 or plan.get("item_width") != 3:  # (a list cut for another kernel)
+          tiles = self._attention_plan(ctx, window, group, 128, num_kv_heads, head_dim, tag=("rows", 128))
+        rc = self._attention_lib(head_dim)[7](*common, _ptr(out), t, *sizes, _ptr(tiles["prefill_items"]),
+                                              tiles["num_prefill"], _ptr(distance_bias), _ptr(self.err), self._stream())
+        self.launches += 1
+        if rc:
+          raise KernelError(f"sb_attn_prefill_tc_biased: {_STATUS.get(rc, rc)}")
       elif plan["num_prefill"] and use_tc:
         rc = prefill_tc(*common, _ptr(out), t, *sizes, _ptr(plan["prefill_items"]), plan["num_prefill"],
                         _ptr(self.err), self._stream())
@@ -1052,7 +1066,7 @@ class CudaOps:
           raise KernelError(f"sb_attn_prefill_tc: {_STATUS.get(rc, rc)}")
       elif plan["num_prefill"] and distance_bias is not None:
         tiles = plan
-        if plan["rows_per_tile"] > 128:  # (a list cut for pairs of blocks, made by a layer without a bias)
+        if plan.get("item_width", 2) != 2:  # (a list cut for the tcgen05 kernels, made by a layer without a bias)
           tiles = self._attention_plan(ctx, window, group, 64, num_kv_heads, head_dim, tag=("rows", 64))
         rc = self._attention_lib(head_dim)[6](
             *common, _ptr(out), *sizes, _ptr(tiles["prefill_items"]), tiles["num_prefill"], tiles["rows_per_tile"],

@@ -217,7 +217,7 @@ def test_biases_rotation_by_halves_and_the_stores(sizes, where):
 
 @pytest.mark.parametrize("where", WHERE)
 @pytest.mark.parametrize("sizes", [(4, 2, 16, 16, 12), (3, 1, 20, 12, 40), (2, 2, 64, 64, 33), (6, 3, 12, 20, 1), (8, 1, 96, 96, 72),
-                                   (8, 2, 64, 64, 200)])
+                                   (8, 2, 64, 64, 200), (4, 2, 128, 128, 100), (16, 1, 64, 64, 50)])
 def test_windowed_attention_with_the_distance_bias(sizes, where):
   """Three sequences side by side: a prompt's portion that starts inside a page with older keys in
   the cache, a single token far into its sequence, and a first portion; keys and values are written
@@ -262,6 +262,14 @@ def test_windowed_attention_with_the_distance_bias(sizes, where):
                             num_kv_heads=kv_heads, head_dim=d, logit_softcap=0.0, window=window,
                             distance_bias=torch.stack([r1, r2]).contiguous(), **more).float().cpu().numpy()
   close(got, np.concatenate(want), dtype, "attention with the distance bias", bf16=2e-2)
+  if hasattr(ops, "prefill_tcgen05"):
+    # once more with the prompt portions on the mma.sync tiles where the tcgen05 kernel took them
+    ops.prefill_tcgen05 = False
+    ctx = context(ops, device, lengths_before, new, slots=slots, tables=[g.tables for g in mgr.groups], page_size=page_size)
+    got = ops.paged_attention(torch.cat(q_rows).contiguous(), storage, ctx.block_tables[0], ctx, num_heads=heads,
+                              num_kv_heads=kv_heads, head_dim=d, logit_softcap=0.0, window=window,
+                              distance_bias=torch.stack([r1, r2]).contiguous(), **more).float().cpu().numpy()
+    close(got, np.concatenate(want), dtype, "attention with the distance bias, mma.sync tiles", bf16=2e-2)
   if hasattr(ops, "check_errors"):
     ops.check_errors()
 
