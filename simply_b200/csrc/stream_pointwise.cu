@@ -21,20 +21,30 @@ scaled_residual_tanh_kernel(float* __restrict__ h, const T* __restrict__ b1, con
                             const float* __restrict__ alpha, const float* __restrict__ w,
                             const float* __restrict__ bias, const int* __restrict__ rows, T* __restrict__ y,
                             int width, int num_rows_total, int* err) {
-  // The factors and the norm's vectors are weights: fetched before the wait for the inputs.
-  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  // A thread owns one 16-byte vector of the branches' and the result's storage type: 4 channels
+  // in float32, 8 in bfloat16 (two vectors of the stream).  The factors and the norm's vectors
+  // are weights: fetched before the wait for the inputs.
+  constexpr int N = Vec<T>::N;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * N;
   const bool on = c0 < width;
-  const bool vec = (width & 3) == 0;
-  float f1[4] = {1.f, 1.f, 1.f, 1.f}, f2[4] = {1.f, 1.f, 1.f, 1.f}, wv[4] = {0.f, 0.f, 0.f, 0.f},
-        bv[4] = {0.f, 0.f, 0.f, 0.f};
+  const bool vec = width % N == 0;
+  float f1[N], f2[N], wv[N], bv[N];
+#pragma unroll
+  for (int k = 0; k < N; ++k) { f1[k] = f2[k] = 1.f; wv[k] = bv[k] = 0.f; }
   const float a = alpha != nullptr ? alpha[0] : 0.f;
   if (on) {
+    if (vec) {
+      if (b1 != nullptr && s1 != nullptr) load_scalars<N>(s1, 1, c0, f1);
+      if (b2 != nullptr && s2 != nullptr) load_scalars<N>(s2, 1, c0, f2);
+      if (y != nullptr) { load_scalars<N>(w, 1, c0, wv); load_scalars<N>(bias, 1, c0, bv); }
+    } else {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      if (c0 + k < width) {
-        if (b1 != nullptr && s1 != nullptr) f1[k] = s1[c0 + k];
-        if (b2 != nullptr && s2 != nullptr) f2[k] = s2[c0 + k];
-        if (y != nullptr) { wv[k] = w[c0 + k]; bv[k] = bias[c0 + k]; }
+      for (int k = 0; k < N; ++k) {
+        if (c0 + k < width) {
+          if (b1 != nullptr && s1 != nullptr) f1[k] = s1[c0 + k];
+          if (b2 != nullptr && s2 != nullptr) f2[k] = s2[c0 + k];
+          if (y != nullptr) { wv[k] = w[c0 + k]; bv[k] = bias[c0 + k]; }
+        }
       }
     }
   }
@@ -47,39 +57,55 @@ scaled_residual_tanh_kernel(float* __restrict__ h, const T* __restrict__ b1, con
     if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_ROW);
     src = 0;
   }
-  float* hp = h + (size_t)src * width + c0;
-  float v[4];
+  const size_t at = (size_t)src * width + c0;
+  float* hp = h + at;
+  float v[N], x1[N], x2[N];
+#pragma unroll
+  for (int k = 0; k < N; ++k) v[k] = x1[k] = x2[k] = 0.f;
+  // every load is issued before the first sum
   if (vec) {
-    Vec<float>::load(hp, v);
+#pragma unroll
+    for (int k = 0; k < N; k += 4) Vec<float>::load(hp + k, v + k);
+    if (b1 != nullptr) Vec<T>::load(b1 + at, x1);
+    if (b2 != nullptr) Vec<T>::load(b2 + at, x2);
   } else {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) v[k] = c0 + k < width ? hp[k] : 0.f;
-  }
-  const bool adds = b1 != nullptr || b2 != nullptr;
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    if (c0 + k < width) {
-      // (the sum of the branches first, then the stream: one order whatever the step holds)
-      float add = 0.f;
-      if (b1 != nullptr) add = f1[k] * to_f32<T>(b1[(size_t)src * width + c0 + k]);
-      if (b2 != nullptr) add = fmaf(f2[k], to_f32<T>(b2[(size_t)src * width + c0 + k]), add);
-      v[k] += add;
+    for (int k = 0; k < N; ++k) {
+      if (c0 + k < width) {
+        v[k] = hp[k];
+        if (b1 != nullptr) x1[k] = to_f32<T>(b1[at + k]);
+        if (b2 != nullptr) x2[k] = to_f32<T>(b2[at + k]);
+      }
     }
   }
-  if (adds && rows == nullptr) {
-    if (vec) {
-      Vec<float>::store(hp, v);
-    } else {
+  const bool adds = b1 != nullptr || b2 != nullptr;
+  if (adds) {
+    // (the sum of the branches first, then the stream: one order whatever the step holds)
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        if (c0 + k < width) hp[k] = v[k];
+    for (int k = 0; k < N; ++k) v[k] += fmaf(f2[k], x2[k], f1[k] * x1[k]);
+    if (rows == nullptr) {
+      if (vec) {
+#pragma unroll
+        for (int k = 0; k < N; k += 4) Vec<float>::store(hp + k, v + k);
+      } else {
+#pragma unroll
+        for (int k = 0; k < N; ++k)
+          if (c0 + k < width) hp[k] = v[k];
+      }
     }
   }
   if (y != nullptr) {
     T* yp = y + (size_t)r * width + c0;
+    float out[N];
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
-      if (c0 + k < width) yp[k] = from_f32<T>(fmaf(tanhf(a * v[k]), wv[k], bv[k]));
+    for (int k = 0; k < N; ++k) out[k] = fmaf(tanhf(a * v[k]), wv[k], bv[k]);
+    if (vec) {
+      Vec<T>::store(yp, out);
+    } else {
+#pragma unroll
+      for (int k = 0; k < N; ++k)
+        if (c0 + k < width) yp[k] = from_f32<T>(out[k]);
+    }
   }
 }
 
@@ -89,8 +115,10 @@ extern "C" int sb_scaled_residual_tanh(float* h, const void* b1, const float* s1
                                        int* err, cudaStream_t stream) {
   if (num_rows == 0 || width == 0) return 0;
   if (y != nullptr && (alpha == nullptr || w == nullptr || bias == nullptr)) return -13;
-  const int threads = width >= 1024 ? 256 : ((width + 3) / 4 + 31) / 32 * 32;
-  const unsigned gx = (unsigned)(((width + 3) / 4 + threads - 1) / threads);
+  const int per = dtype == SB_DTYPE_F32 ? 4 : 8;  // channels per thread: one 16-byte vector of T
+  const int lanes = (width + per - 1) / per;
+  const int threads = lanes >= 256 ? 256 : (lanes + 31) / 32 * 32;
+  const unsigned gx = (unsigned)((lanes + threads - 1) / threads);
   for (int r0 = 0; r0 < num_rows; r0 += 65535) {
     const int n = min(65535, num_rows - r0);
     const dim3 grid(gx, (unsigned)n);
