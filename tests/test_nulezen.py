@@ -121,6 +121,23 @@ def test_long_prompts_pages_of_64_and_head_sizes_of_the_tensor_core_kernels(dtyp
   engine.ops.check_errors()
 
 
+@pytest.mark.parametrize("where", WHERE)
+def test_many_query_heads_per_kv_head(where):
+  """32 and 12 query heads per kv head: a single token's rows no longer fit the split-key kernel's
+  16, so decoded tokens take the tile kernels too."""
+  cfg_dict = nx.config(
+      [nx.biased(heads=32, kv_heads=1, dim=64, vdim=64, window=50, scale=0.12),
+       nx.rotated(heads=24, kv_heads=2, dim=32, vdim=32, dims=16, window=31, scale=0.2),
+       nx.biased(heads=20, kv_heads=1, dim=16, vdim=16, window=40, scale=0.25)],
+      [nx.dense(ff=64), None, nx.moe(experts=4, top=2, ff=32, shared=0)], width=64, vocab=90, loop=(0, 2, 2))
+  engine, t = engine_for(cfg_dict, where, seed=8, page_size=16, max_seq_len=128)
+  toks = tokens_for(cfg_dict, 90, 2)
+  want = plain.forward(cfg_dict, nx.as_numpy(t), toks)
+  for what, cuts in [("whole", [90]), ("decoding", [60] + [1] * 30), ("portions", nx.cuts_of(90, [17, 2, 40, 3]))]:
+    nx.check_close(nx.run_cuts(engine, toks, cuts), want, where[0], what)
+  engine.ops.check_errors()
+
+
 # ---- a key that stands out: far back, at a page's border, either side of the window's edge -----------
 
 @pytest.mark.parametrize("where", WHERE)
