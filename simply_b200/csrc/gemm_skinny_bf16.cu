@@ -13,7 +13,9 @@
 // transposition is needed.  A block owns 16 weight rows; its warps split K and
 // add their partial sums through shared memory in a fixed order.
 //
-// Epilogues: 0 store as bfloat16; 1 store float32 with an optional soft cap
+// Epilogues: 0 store as bfloat16, with `act` 5 after the activation xielu(z) = a z^2 + z/2 for z > 0,
+// b (e^z - 1 - z) + z/2 otherwise (a in `cap`, b in `rs.act_b`: the host's softplus of the layer's two
+// learned numbers); 1 store float32 with an optional soft cap
 // (simply/model_lib.py:107-109, the output layer); 2 gated activation: the block
 // also owns rows [N/2 + n0, N/2 + n0 + 16) and stores act(gate) * up
 // (simply/model_lib.py:722-726); 3 the fused q, k, v projection of an attention layer: a block
@@ -35,6 +37,7 @@ struct RopeStore {
   const int* positions;
   int num_q_heads, num_kv_proj, head_dim, page_size, num_pages;
   int* err;
+  float act_b;  // epilogue 0 with an activation: its second number
 };
 
 __device__ __forceinline__ float skinny_activation(float g, int act) {
@@ -219,7 +222,13 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void*
         dst[j + half] = __float2bfloat16_rn(b);
       }
     } else if (EPI == 0) {
-      reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(v[0]);
+      float z = v[0];
+      if (act == 5) {
+        // Round to bfloat16 first, as the unfused path stores the product before it activates.
+        z = __bfloat162float(__float2bfloat16_rn(z));
+        z = z > 0.f ? fmaf(cap * z, z, 0.5f * z) : fmaf(rs.act_b, expm1f(z) - z, 0.5f * z);
+      }
+      reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(z);
     } else if (EPI == 1) {
       reinterpret_cast<float*>(out)[o] = cap > 0.f ? cap * tanhf(v[0] / cap) : v[0];
     } else {
@@ -271,8 +280,8 @@ static int launch_skinny(const bf16* x, const bf16* w, void* out, int M, int N, 
 
 // Returns -9 when the shape is outside what the kernel takes (the caller then
 // uses the library product): M > 32, K not a multiple of 8, N odd for the gated epilogue.
-extern "C" int sb_gemm_skinny_bf16(const void* x, const void* w, void* out, int M, int N, int K, int epilogue,
-                                   float cap, int act, int warps_override, cudaStream_t stream) {
+static int skinny_dispatch(const void* x, const void* w, void* out, int M, int N, int K, int epilogue,
+                           float cap, int act, int warps_override, cudaStream_t stream, const RopeStore& rs) {
   if (M == 0 || N == 0) return 0;
   if (M > 32 || K % 8 != 0 || K <= 0 || epilogue < 0 || epilogue > 2) return -9;
   if (epilogue == 2 && (N % 2 != 0 || act < 0 || act > 3)) return -9;
@@ -288,18 +297,31 @@ extern "C" int sb_gemm_skinny_bf16(const void* x, const void* w, void* out, int 
   if (K < warps * 32 * 4) warps = K >= 8 * 32 * 4 ? 8 : 4;  // every warp should have a full batch of loads
   if (warps_override == 4 || warps_override == 8 || warps_override == 16) warps = warps_override;
   if (M <= 8) {
-    if (warps == 16) return launch_skinny<1, 16>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
-    if (warps == 8) return launch_skinny<1, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
-    return launch_skinny<1, 4>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+    if (warps == 16) return launch_skinny<1, 16>(xp, wp, out, M, N, K, epilogue, cap, act, stream, rs);
+    if (warps == 8) return launch_skinny<1, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream, rs);
+    return launch_skinny<1, 4>(xp, wp, out, M, N, K, epilogue, cap, act, stream, rs);
   }
   if (M <= 16) {
-    if (warps == 16) return launch_skinny<2, 16>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
-    if (warps == 8) return launch_skinny<2, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
-    return launch_skinny<2, 4>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+    if (warps == 16) return launch_skinny<2, 16>(xp, wp, out, M, N, K, epilogue, cap, act, stream, rs);
+    if (warps == 8) return launch_skinny<2, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream, rs);
+    return launch_skinny<2, 4>(xp, wp, out, M, N, K, epilogue, cap, act, stream, rs);
   }
   // (8 warps at most: with 16 the partial sums of the gated epilogue outgrow static shared memory.)
-  if (warps == 4) return launch_skinny<4, 4>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
-  return launch_skinny<4, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream);
+  if (warps == 4) return launch_skinny<4, 4>(xp, wp, out, M, N, K, epilogue, cap, act, stream, rs);
+  return launch_skinny<4, 8>(xp, wp, out, M, N, K, epilogue, cap, act, stream, rs);
+}
+
+extern "C" int sb_gemm_skinny_bf16(const void* x, const void* w, void* out, int M, int N, int K, int epilogue,
+                                   float cap, int act, int warps_override, cudaStream_t stream) {
+  return skinny_dispatch(x, w, out, M, N, K, epilogue, cap, act, warps_override, stream, RopeStore{});
+}
+
+// x . w^T, then xielu with the numbers a (z > 0) and b (z <= 0), stored as bfloat16.
+extern "C" int sb_gemm_skinny_bf16_xielu(const void* x, const void* w, void* out, int M, int N, int K, float a,
+                                         float b, int warps_override, cudaStream_t stream) {
+  RopeStore rs{};
+  rs.act_b = b;
+  return skinny_dispatch(x, w, out, M, N, K, 0, a, 5, warps_override, stream, rs);
 }
 
 // The fused q, k, v projection of an attention layer for at most 16 tokens: product, rotation,

@@ -239,6 +239,7 @@ class CudaOps:
         "sb_soft_cap": [c_void, c_float, c_ll, c_void],
         "sb_gemm_f32_nt": [c_void, c_void, c_void, c_int, c_int, c_int, c_float, c_void],
         "sb_gemm_skinny_bf16": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void],
+        "sb_gemm_skinny_bf16_xielu": [c_void, c_void, c_void, c_int, c_int, c_int, c_float, c_float, c_int, c_void],
         "sb_gemm_stream_tc": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                               c_void, c_void],
         "sb_gemm_gated_tc": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void, c_void],
@@ -880,8 +881,18 @@ class CudaOps:
       self._call("sb_add_row", _ptr(out), _ptr(row), out.shape[0], out.shape[1])
     return out
 
-  def linear_xielu(self, x: torch.Tensor, w: torch.Tensor, act: torch.Tensor) -> torch.Tensor:
-    """xielu(x . w^T) with the activation's two learned numbers `act` (float32 [2])."""
+  def linear_xielu(self, x: torch.Tensor, w: torch.Tensor, act: torch.Tensor,
+                   factors: tuple[float, float] | None = None) -> torch.Tensor:
+    """xielu(x . w^T) with the activation's two learned numbers `act` (float32 [2]).  `factors`:
+    (softplus(act[0]), 1/2 + softplus(act[1])) as the host knows them; with them a step of few
+    tokens activates on the product's sums (csrc/gemm_skinny_bf16.cu)."""
+    m, k = x.shape
+    if (factors is not None and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+        and m <= self.skinny_max_rows):
+      out = self._new(m, w.shape[0], dtype=torch.bfloat16)
+      if self._call("sb_gemm_skinny_bf16_xielu", _ptr(x), _ptr(w), _ptr(out), m, w.shape[0], k, float(factors[0]),
+                    float(factors[1]), self.skinny_warps) == 0:
+        return out
     z = self.linear(x, w)
     self._call("sb_xielu", _ptr(z), _ptr(act), _ptr(z), _code(z), z.numel())
     return z

@@ -9,6 +9,7 @@ g' = min(g, L), u' = clamp(u, -L, L), z = g' sigmoid(1.702 g') (u' + 1).
 
 from __future__ import annotations
 
+import math
 from typing import Any
 
 import torch
@@ -87,6 +88,7 @@ class LearnedActivationFeedForward(FeedForward):
     self.down_proj = Linear(f"{prefix}.{names.get('down', 'down')}", width, hidden)
     self.act_name = f"{prefix}.{names.get('act', 'act')}"
     self.act: torch.Tensor | None = None
+    self.factors: tuple[float, float] | None = None
 
   def tensor_specs(self) -> list[TensorSpec]:
     return [self.up_proj.spec(), self.down_proj.spec(), TensorSpec(self.act_name, (2,), "scale", precision="stored")]
@@ -95,9 +97,13 @@ class LearnedActivationFeedForward(FeedForward):
     self.up_proj.bind(tensors)
     self.down_proj.bind(tensors)
     self.act = tensors[self.act_name].float().contiguous()
+    # (weights: known to the host once, so that a kernel can take them as plain numbers)
+    p, q = (float(v) for v in self.act.double().cpu())
+    softplus = lambda z: math.log1p(math.exp(-abs(z))) + max(z, 0.0)
+    self.factors = (softplus(p), 0.5 + softplus(q))
 
   def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
-    return self.down_proj(ctx.ops.linear_xielu(x, self.up_proj.weight, self.act), ctx)
+    return self.down_proj(ctx.ops.linear_xielu(x, self.up_proj.weight, self.act, self.factors), ctx)
 
 
 @FEED_FORWARDS.register("none")

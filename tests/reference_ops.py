@@ -130,7 +130,7 @@ class ReferenceOps:
     out = x.float() @ w.float().t()
     return out + row.float() if row is not None else out
 
-  def linear_xielu(self, x, w, act):
+  def linear_xielu(self, x, w, act, factors=None):
     z = self.linear(x, w).float()
     ap = torch.nn.functional.softplus(act[0].float())
     an = 0.5 + torch.nn.functional.softplus(act[1].float())

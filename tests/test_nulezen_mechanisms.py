@@ -103,6 +103,11 @@ def test_the_learned_activation(rows, width, hidden, where):
     if dtype == torch.bfloat16:  # (the product is stored in bfloat16 before the activation)
       z = torch.from_numpy(z).to(torch.bfloat16).double().numpy()
     close(got, plain.xielu(z, p, q), dtype, f"xielu with p {p}, q {q}")
+    # with the host's factors a step of few tokens activates on the product's sums
+    factors = (plain.softplus(p), 0.5 + plain.softplus(q))
+    for n in (1, min(rows, 9), min(rows, 16), rows):
+      got = ops.linear_xielu(x[:n].contiguous(), up, f32([p, q], device), factors).float().cpu().numpy()
+      close(got, plain.xielu(z[:n], p, q), dtype, f"xielu with p {p}, q {q}, {n} rows, factors from the host")
   z = np.linspace(-30.0, 12.0, 85).reshape(1, -1)
   for v in (-1e-3, 0.0, 1e-3):
     z[0, int(abs(v) * 1e3) + 3] = v
