@@ -53,7 +53,7 @@ def config(layers, mlps, width=48, vocab=97, embed_scale=3.0, logit_scale=0.7, l
     layer["mlp"] = copy.deepcopy(mlp)
     out.append(layer)
   d = {"architecture": "Nulezen", "vocab": vocab, "width": width, "embedding": {"scale": embed_scale},
-       "logit_scale": logit_scale, "norm": {"eps": 1e-5}, "layers": out, "max_context": 512}
+       "logit_scale": logit_scale, "norm": {"eps": 1e-6}, "layers": out, "max_context": 512}
   if loop is not None:
     d["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
   return d

@@ -106,7 +106,7 @@ def test_long_prompts_pages_of_64_and_head_sizes_of_the_tensor_core_kernels(dtyp
   a page and that span several, more routed rows per expert than one tile holds."""
   cfg_dict = nx.config(
       [nx.biased(heads=8, kv_heads=2, dim=64, vdim=64, window=150, scale=0.1),
-       nx.rotated(heads=6, kv_heads=1, dim=96, vdim=96, dims=96, base=5000.0, window=72, scale=0.09),
+       nx.rotated(heads=12, kv_heads=2, dim=96, vdim=96, dims=96, base=5000.0, window=80, scale=0.09),
        nx.rotated(heads=4, kv_heads=2, dim=128, vdim=128, dims=64, window=300, scale=0.07),
        nx.biased(heads=4, kv_heads=4, dim=32, vdim=48, window=65, scale=0.15)],
       [nx.moe(experts=3, top=2, ff=96, shared=128), nx.dense(ff=256), nx.moe(experts=8, top=4, ff=32, shared=0), None],

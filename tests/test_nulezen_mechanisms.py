@@ -28,7 +28,7 @@ def f32(x, device):
 # ---- the norm without statistics, branches with a factor per channel ------------------------------------
 
 @pytest.mark.parametrize("where", WHERE)
-@pytest.mark.parametrize("rows,width", [(5, 32), (3, 37), (70, 192), (2, 1030), (1, 6)])
+@pytest.mark.parametrize("rows,width", [(5, 32), (3, 37), (70, 200), (2, 1030), (1, 6)])
 def test_scaled_branches_and_the_tanh_norm(rows, width, where):
   ops, dtype = table(where)
   device = where[1]
@@ -165,7 +165,7 @@ def test_routing_by_the_largest_logits_and_the_clamped_experts(sizes, where):
 
 @pytest.mark.parametrize("where", WHERE)
 @pytest.mark.parametrize("sizes", [(4, 2, 16, 16, 8, True), (3, 1, 20, 12, 20, True), (2, 2, 64, 64, 0, False), (6, 3, 12, 20, 4, True),
-                                   (8, 1, 96, 96, 96, True)])
+                                   (10, 2, 96, 96, 48, True)])
 def test_biases_rotation_by_halves_and_the_stores(sizes, where):
   heads, kv_heads, d, dv, dims, with_bias = sizes
   ops, dtype = table(where)
@@ -221,7 +221,7 @@ def test_biases_rotation_by_halves_and_the_stores(sizes, where):
 
 
 @pytest.mark.parametrize("where", WHERE)
-@pytest.mark.parametrize("sizes", [(4, 2, 16, 16, 12), (3, 1, 20, 12, 40), (2, 2, 64, 64, 33), (6, 3, 12, 20, 1), (8, 1, 96, 96, 72),
+@pytest.mark.parametrize("sizes", [(4, 2, 16, 16, 12), (3, 1, 20, 12, 40), (2, 2, 64, 64, 33), (6, 3, 12, 20, 1), (10, 2, 96, 96, 70),
                                    (8, 2, 64, 64, 200), (4, 2, 128, 128, 100), (16, 1, 64, 64, 50), (32, 1, 64, 64, 90)])
 def test_windowed_attention_with_the_distance_bias(sizes, where):
   """Three sequences side by side: a prompt's portion that starts inside a page with older keys in
