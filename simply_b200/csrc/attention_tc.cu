@@ -80,6 +80,9 @@ struct TcParams {
   // optional, float32 [2, Hq]: r1 and r2 per query head; the score of query i and key j loses
   // r1 log(1 + r2 (i - j)) (not together with a cap)
   const float* distance;
+  // 1: the block first writes the term for every (distance, head of its kv head) into shared memory
+  // behind the tiles, [window][group] floats, and the softmax threads read it there
+  int bias_table;
   const int* items;  // per block, in launch order: (sequence, first token of the tile of 128 / G tokens, kv head)
   int box_rows;      // rows per key/value TMA box: min(page_size, 64)
   int* err;
@@ -147,6 +150,15 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     mbar_init(&o_done, 1);
     s_failed = 0;
     mbar_fence_init();
+  }
+  // The distance term depends on (head, distance) alone: with a window that fits, a table of it
+  // spares the softmax threads a logarithm per score (the special-function pipe is their busiest).
+  float* bias_tab = reinterpret_cast<float*>(sv + V_STAGES * KV_TILE_BYTES);
+  if (p.bias_table) {
+    for (int i = threadIdx.x; i < p.window * group; i += TC_THREADS) {
+      const int d = i / group, h = m * group + (i - d * group);
+      bias_tab[i] = p.distance[h] * 0.6931471805599453f * __log2f(fmaf(p.distance[p.num_q_heads + h], (float)d, 1.0f));
+    }
   }
   if (warp == 1) tmem_alloc(&tmem_slot, TMEM_COLS);
   tc_fence_before_sync();
@@ -303,7 +315,9 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
     const float scale2 = p.cap > 0.f ? p.cap * LOG2E : LOG2E;  // from x (tanh's value, or the score) to log2 units
     // The distance bias of this thread's row: r1 ln 2 and r2 of its head.
     const bool biased = p.distance != nullptr;
-    const int head = m * group + (r < rows_valid ? r % group : 0);
+    const bool tabled = p.bias_table != 0;
+    const int head_in_group = r < rows_valid ? r % group : 0;
+    const int head = m * group + head_in_group;
     const float bias_r1 = biased ? p.distance[head] * 0.6931471805599453f : 0.f;
     const float bias_r2 = biased ? p.distance[p.num_q_heads + head] : 0.f;
     float m_own = -INFINITY, l = 0.f;  // the maximum this thread's sum is relative to; the sum
@@ -345,7 +359,11 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
           float v = __uint_as_float(sr[c]);
           if (p.cap > 0.f) v = fast_tanh(v * inv_cap);
           const int key = j0 + part * CW + c;
-          if (biased) v -= bias_r1 * __log2f(fmaf(bias_r2, (float)max(pos - key, 0), 1.0f));
+          if (biased) {
+            const int d = max(pos - key, 0);
+            v -= tabled ? bias_tab[min(d, p.window - 1) * group + head_in_group]
+                        : bias_r1 * __log2f(fmaf(bias_r2, (float)d, 1.0f));
+          }
           v = (key <= pos && (p.window <= 0 || pos - key < p.window)) ? v : -INFINITY;
           sr[c] = __float_as_uint(v);
           mx = fmaxf(mx, v);
@@ -355,7 +373,10 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
         for (int c = 0; c < CW; ++c) {
           float v = __uint_as_float(sr[c]);
           if (p.cap > 0.f) v = fast_tanh(v * inv_cap);
-          if (biased) v -= bias_r1 * __log2f(fmaf(bias_r2, (float)(pos - (j0 + part * CW + c)), 1.0f));
+          if (biased) {
+            const int d = pos - (j0 + part * CW + c);  // every key is visible: 0 <= d < window
+            v -= tabled ? bias_tab[d * group + head_in_group] : bias_r1 * __log2f(fmaf(bias_r2, (float)d, 1.0f));
+          }
           sr[c] = __float_as_uint(v);
           mx = fmaxf(mx, v);
         }
@@ -522,6 +543,10 @@ attn_prefill_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap map
 }
 
 constexpr size_t TC_SMEM = (size_t)Q_BYTES + (K_STAGES + V_STAGES) * KV_TILE_BYTES + 1024;
+// Room for the table of distance terms behind the tiles: what a block may have (227 KB) less its
+// static shared memory, 48 KB at most.
+constexpr size_t TC_SMEM_LIMIT = 232448 - 6144;
+constexpr size_t TC_TABLE_MAX = TC_SMEM_LIMIT <= TC_SMEM ? 0 : (TC_SMEM_LIMIT - TC_SMEM < 48 * 1024 ? TC_SMEM_LIMIT - TC_SMEM : 48 * 1024);
 static_assert(QT_DIMS == 0 || QT_DIMS / (GROUPS * SPLIT) == 32, "each softmax thread stores 32 dims of Q");
 static_assert(V_STAGES == 2, "the zeroing of value rows looks two tiles back");
 
@@ -567,13 +592,23 @@ static int prefill_tc_launch(const void* q, const void* cache, const int* block_
   p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
   p.cap = cap; p.window = window; p.items = items; p.box_rows = box_rows; p.err = err;
   p.distance = distance;
+  size_t table_bytes = 0;
+  static int table_allowed = -1;  // SIMPLY_B200_BIAS_TABLE=0: every softmax thread computes its terms (experiments)
+  if (table_allowed < 0) {
+    const char* e = getenv("SIMPLY_B200_BIAS_TABLE");
+    table_allowed = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (table_allowed && distance != nullptr && window > 0 && (size_t)window * group * sizeof(float) <= TC_TABLE_MAX)
+    table_bytes = (size_t)window * group * sizeof(float);
+  p.bias_table = table_bytes > 0 ? 1 : 0;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(TC_SMEM + TC_TABLE_MAX));
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  sb_launch(attn_prefill_tc_kernel, dim3(num_items), TC_THREADS, TC_SMEM, stream, p, map_q, map_kv, map_out);
+  sb_launch(attn_prefill_tc_kernel, dim3(num_items), TC_THREADS, TC_SMEM + table_bytes, stream, p, map_q, map_kv, map_out);
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -222,7 +222,8 @@ def test_biases_rotation_by_halves_and_the_stores(sizes, where):
 
 @pytest.mark.parametrize("where", WHERE)
 @pytest.mark.parametrize("sizes", [(4, 2, 16, 16, 12), (3, 1, 20, 12, 40), (2, 2, 64, 64, 33), (6, 3, 12, 20, 1), (10, 2, 96, 96, 70),
-                                   (8, 2, 64, 64, 200), (4, 2, 128, 128, 100), (16, 1, 64, 64, 50), (32, 1, 64, 64, 90)])
+                                   (8, 2, 64, 64, 200), (4, 2, 128, 128, 100), (16, 1, 64, 64, 50), (32, 1, 64, 64, 90),
+                                   (8, 2, 64, 64, 4000)])
 def test_windowed_attention_with_the_distance_bias(sizes, where):
   """Three sequences side by side: a prompt's portion that starts inside a page with older keys in
   the cache, a single token far into its sequence, and a first portion; keys and values are written
